@@ -1,0 +1,293 @@
+// Host side of libeo_b200.so: argument checks, TMA descriptor construction and kernel launches
+// behind the C ABI declared in include/eo_b200.h.
+#include "../../include/eo_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "elementwise.cuh"
+#include "gemm_sm100.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define EO_CUDA(call)                                                                              \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess) return fail(EO_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+// Kernels report bounded-wait failures here; one copy per device that loads the module.
+__device__ unsigned int g_device_status = 0;
+
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  unsigned int* status_ptr = nullptr;
+};
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_mu;
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+int device_setup(DeviceInfo** out) {
+  int dev = 0;
+  EO_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(EO_ERR_BAD_ARG, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    cudaDeviceProp prop;
+    EO_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      return fail(EO_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library runs on sm_100 only", dev, prop.major,
+                  prop.minor);
+    d.sm_count = prop.multiProcessorCount;
+    EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_device_status));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kGemmSmemBytes));
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      EO_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (fn == nullptr || qres != cudaDriverEntryPointSuccess)
+        return fail(EO_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    }
+    d.ready = true;
+  }
+  *out = &d;
+  return EO_OK;
+}
+
+// 3-D tiled map over a batch of row-major matrices: dims {inner, rows, batch}, 128-byte swizzle,
+// box {box_inner, box_rows, 1}.  Out-of-range parts of a box read as zero.
+int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner, uint64_t rows, uint64_t batch,
+             int64_t ld, int64_t stride, uint32_t box_inner, uint32_t box_rows) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(EO_ERR_BAD_ARG, "operand base not 16-byte aligned");
+  if ((ld * elem_bytes) % 16 != 0)
+    return fail(EO_ERR_BAD_ARG, "leading dimension %lld not a multiple of 16 bytes", (long long)ld);
+  if (batch > 1 && (stride * elem_bytes) % 16 != 0)
+    return fail(EO_ERR_BAD_ARG, "batch stride %lld not a multiple of 16 bytes", (long long)stride);
+  if (ld < static_cast<int64_t>(inner)) return fail(EO_ERR_BAD_ARG, "leading dimension smaller than row length");
+  cuuint64_t dims[3] = {inner, rows, batch};
+  const uint64_t bstride = (batch > 1) ? static_cast<uint64_t>(stride) : rows * static_cast<uint64_t>(ld);
+  cuuint64_t strides[2] = {static_cast<uint64_t>(ld) * elem_bytes, bstride * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = (elem_bytes == 2) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = g_encode(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EO_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return EO_OK;
+}
+
+int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, const void* B, int b_mn, int64_t ldb,
+                int64_t strideB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
+                int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
+                int round_bf16, int tri, int skip_upper, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (precision != 0 && precision != 1) return fail(EO_ERR_BAD_ARG, "precision must be 0 (bf16) or 1 (tf32)");
+  if (precision == 1 && !d_fp32) return fail(EO_ERR_BAD_ARG, "tf32 precision needs an fp32 output");
+  if (beta != 0.0f && C == nullptr) return fail(EO_ERR_BAD_ARG, "beta != 0 needs C");
+  if (A == nullptr || B == nullptr || D == nullptr) {
+    if (batch == 0 || M == 0 || N == 0) return EO_OK;
+    return fail(EO_ERR_BAD_ARG, "null operand");
+  }
+  if (batch == 0 || M == 0 || N == 0) return EO_OK;
+  if (K == 0) return fail(EO_ERR_BAD_ARG, "K == 0 is not supported");
+
+  const int eb = precision == 0 ? 2 : 4;
+  const int bk = eo::kRowBytes / eb;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn)
+    rc = make_map(&tmA, A, eb, K, M, batch, lda, strideA, bk, eo::kBlockM);
+  else
+    rc = make_map(&tmA, A, eb, M, K, batch, lda, strideA, bk, bk);
+  if (rc) return rc;
+  if (!b_mn)
+    rc = make_map(&tmB, B, eb, K, N, batch, ldb, strideB, bk, eo::kBlockM);
+  else
+    rc = make_map(&tmB, B, eb, N, K, batch, ldb, strideB, bk, bk);
+  if (rc) return rc;
+
+  eo::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.batch = batch;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
+  p.tf32 = precision;
+  p.tri = tri;
+  p.skip_upper = skip_upper;
+  p.c_fp32 = precision;
+  p.d_fp32 = d_fp32;
+  p.round_bf16 = round_bf16;
+  p.C = (beta != 0.0f) ? C : nullptr;
+  p.ldc = ldc;
+  p.strideC = strideC;
+  p.D = D;
+  p.ldd = ldd;
+  p.strideD = strideD;
+  p.alpha = alpha;
+  p.beta = beta;
+  p.post_scale = post_scale;
+  p.status = dev->status_ptr;
+
+  // Descriptor geometry.  K-major: rows of 128 bytes along K, eight-row groups 1024 bytes apart,
+  // each MMA consumes 32 bytes of a row.  MN-major: rows of 128 bytes along M/N (one per k),
+  // eight-k groups 1024 bytes apart, 128-byte-wide M/N atoms bk rows apart; each MMA consumes
+  // 32 / elem_bytes k-rows.
+  const unsigned int mn_adv = static_cast<unsigned int>((32 / eb) * eo::kRowBytes);
+  const unsigned int mn_lbo = static_cast<unsigned int>(bk * eo::kRowBytes);
+  p.adv_a = a_mn ? mn_adv : 32u;
+  p.adv_b = b_mn ? mn_adv : 32u;
+  p.lbo_a = a_mn ? mn_lbo : 0u;
+  p.lbo_b = b_mn ? mn_lbo : 0u;
+  p.sbo_a = 1024u;
+  p.sbo_b = 1024u;
+#ifdef EO_BRINGUP
+  if (const char* e = getenv("EO_DBG_MN_LBO")) { if (a_mn) p.lbo_a = atoi(e); if (b_mn) p.lbo_b = atoi(e); }
+  if (const char* e = getenv("EO_DBG_MN_SBO")) { if (a_mn) p.sbo_a = atoi(e); if (b_mn) p.sbo_b = atoi(e); }
+  if (const char* e = getenv("EO_DBG_MN_ADV")) { if (a_mn) p.adv_a = atoi(e); if (b_mn) p.adv_b = atoi(e); }
+  if (const char* e = getenv("EO_DBG_K_LBO")) { if (!a_mn) p.lbo_a = atoi(e); if (!b_mn) p.lbo_b = atoi(e); }
+#endif
+
+  const int c_eb = p.c_fp32 ? 4 : 2;
+  const int d_eb = p.d_fp32 ? 4 : 2;
+  bool vec = (reinterpret_cast<uintptr_t>(D) % 16 == 0) && ((ldd * d_eb) % 16 == 0) && ((strideD * d_eb) % 16 == 0);
+  if (p.C != nullptr)
+    vec = vec && (reinterpret_cast<uintptr_t>(C) % 16 == 0) && ((ldc * c_eb) % 16 == 0) &&
+          ((strideC * c_eb) % 16 == 0);
+  p.vec_ok = vec ? 1 : 0;
+
+  // Tile width: 256 unless the problem is narrow or the wider tile leaves SMs idle.
+  p.tiles_m = (M + eo::kBlockM - 1) / eo::kBlockM;
+  auto count_tiles = [&](int bn, int* tiles_n) {
+    *tiles_n = (N + bn - 1) / bn;
+    if (!tri) return p.tiles_m * (*tiles_n);
+    int total = 0;
+    const int ratio = bn / eo::kBlockM;
+    for (int j = 0; j < *tiles_n; ++j) total += p.tiles_m - j * ratio;
+    return total;
+  };
+  int tn256 = 0, tn128 = 0;
+  const long long t256 = static_cast<long long>(count_tiles(256, &tn256)) * batch;
+  const long long t128 = static_cast<long long>(count_tiles(128, &tn128)) * batch;
+  const bool narrow = (N <= 128) || (t256 < dev->sm_count && t128 > t256);
+  p.bn = narrow ? 128 : 256;
+  p.tiles_n = narrow ? tn128 : tn256;
+  const long long total = narrow ? t128 : t256;
+  if (total > 0x7fffffffLL) return fail(EO_ERR_BAD_ARG, "too many tiles");
+  p.total_tiles = static_cast<int>(total);
+  p.tiles_per_batch = p.total_tiles / batch;
+
+  const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
+  eo::eo_gemm_kernel<<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* eo_version(void) { return "eo_b200 0.1.0 sm_100a"; }
+
+const char* eo_last_error(void) { return g_err; }
+
+int eo_read_device_status(uint32_t* host_code, void* stream) {
+  if (host_code == nullptr) return fail(EO_ERR_BAD_ARG, "host_code is NULL");
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EO_CUDA(cudaStreamSynchronize(s));
+  unsigned int code = 0;
+  EO_CUDA(cudaMemcpyAsync(&code, dev->status_ptr, sizeof(code), cudaMemcpyDeviceToHost, s));
+  EO_CUDA(cudaStreamSynchronize(s));
+  if (code != 0) {
+    EO_CUDA(cudaMemsetAsync(dev->status_ptr, 0, sizeof(code), s));
+    EO_CUDA(cudaStreamSynchronize(s));
+  }
+  *host_code = code;
+  return EO_OK;
+}
+
+int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA, const void* B, int b_mn_major, int64_t ldb,
+            int64_t strideB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
+            int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
+            int round_bf16, void* stream) {
+  return launch_gemm(A, a_mn_major, lda, strideA, B, b_mn_major, ldb, strideB, C, ldc, strideC, D, ldd, strideD, batch,
+                     M, N, K, alpha, beta, post_scale, precision, d_fp32, round_bf16, /*tri=*/0, /*skip_upper=*/0,
+                     stream);
+}
+
+int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA, const void* C, int64_t ldc, int64_t strideC,
+            void* D, int64_t ldd, int64_t strideD, int batch, int N, int K, float alpha, float beta, int skip_upper,
+            int precision, void* stream) {
+  return launch_gemm(A, a_trans, lda, strideA, A, a_trans, lda, strideA, C, ldc, strideC, D, ldd, strideD, batch, N, N,
+                     K, alpha, beta, 1.0f, precision, /*d_fp32=*/precision, /*round_bf16=*/0, /*tri=*/1, skip_upper,
+                     stream);
+}
+
+size_t eo_sumsq_scratch_bytes(int batch, int64_t rows, int64_t cols) {
+  if (batch <= 0) return 0;
+  return static_cast<size_t>(batch) * eo::sumsq_blocks_per_matrix(rows, cols) * sizeof(double);
+}
+
+int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride, double* sumsq,
+                 void* scratch, size_t scratch_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (batch == 0) return EO_OK;
+  if (sumsq == nullptr) return fail(EO_ERR_BAD_ARG, "sumsq is NULL");
+  if (ld < cols) return fail(EO_ERR_BAD_ARG, "ld smaller than cols");
+  const size_t need = eo_sumsq_scratch_bytes(batch, rows, cols);
+  if (scratch_bytes < need || (need > 0 && scratch == nullptr))
+    return fail(EO_ERR_WORKSPACE, "sumsq scratch: need %zu bytes, got %zu", need, scratch_bytes);
+  if (rows > 0 && cols > 0 && x == nullptr) return fail(EO_ERR_BAD_ARG, "x is NULL");
+  eo::launch_sumsq(x, batch, rows, cols, ld, stride, sumsq, static_cast<double*>(scratch),
+                   static_cast<cudaStream_t>(stream));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_normalize_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                     const double* sumsq, float eps, int clamp_eps, void* out, int64_t ldo, int64_t strideo,
+                     int out_fp32, int round_bf16, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (batch == 0 || rows == 0 || cols == 0) return EO_OK;
+  if (x == nullptr || out == nullptr || sumsq == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (ld < cols || ldo < cols) return fail(EO_ERR_BAD_ARG, "leading dimension smaller than cols");
+  eo::launch_normalize(x, batch, rows, cols, ld, stride, sumsq, eps, clamp_eps, out, ldo, strideo, out_fp32,
+                       round_bf16, static_cast<cudaStream_t>(stream));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,388 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:
+//
+//     D[b] = alpha * op(A[b]) * op(B[b])^T + beta * C[b]            (fp32 accumulation in TMEM)
+//
+// with A given as (M x K), B as (N x K); each operand may be stored K-major (K contiguous) or
+// MN-major (M/N contiguous).  With `tri` set the problem is a symmetric rank-k update (A == B,
+// M == N): only tiles touching the lower triangle are computed, the lower part is stored and,
+// unless `skip_upper`, mirrored into the upper part, so that every output element is written once.
+//
+// One CTA per SM, 192 threads:
+//   warp 0      TMA producer   (global -> 128B-swizzled shared-memory ring, kStages deep)
+//   warp 1      MMA issuer     (one elected thread issues tcgen05.mma, accumulators in TMEM)
+//   warps 2..5  epilogue       (tcgen05.ld -> alpha/beta -> round -> global stores)
+// TMEM holds two 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the main loop of
+// tile t+1.  Every wait is bounded; a wait that runs out records a code in the status word and the
+// role leaves its loop.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "sm100_ptx.cuh"
+
+namespace eo {
+
+constexpr int kBlockM = 128;
+constexpr int kMaxBlockN = 256;
+constexpr int kRowBytes = 128;  // one swizzle row: 64 bf16 or 32 fp32 along the contiguous dimension
+constexpr int kStages = 4;
+constexpr int kStageABytes = kBlockM * kRowBytes;     // 16 KiB
+constexpr int kStageBBytes = kMaxBlockN * kRowBytes;  // 32 KiB
+constexpr int kStageBytes = kStageABytes + kStageBBytes;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;  // row-block group height of the general tile order
+
+// Shared-memory budget: ring + barriers + TMEM address slot, plus slack for 1024-byte alignment.
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + 1024;
+
+struct GemmParams {
+  int batch, M, N, K;
+  int bn;          // tile width: 128 or 256
+  int a_mn, b_mn;  // operand stored MN-major (1) or K-major (0)
+  int tf32;        // 0: bf16 operands (kind::f16); 1: fp32 storage read as tf32 (kind::tf32)
+  int tri;         // symmetric update: lower-triangle tiles only
+  int skip_upper;  // with tri: do not mirror into the upper triangle
+  int c_fp32;      // element type of C: fp32 (1) or bf16 (0)
+  int d_fp32;      // element type of D
+  int round_bf16;  // with d_fp32: round the result to bf16 before widening (keeps the bf16 rounding point)
+  int vec_ok;      // C/D rows are 16-byte aligned: the full-chunk fast path may use vector accesses
+  const void* C;
+  long long ldc, strideC;
+  void* D;
+  long long ldd, strideD;
+  float alpha, beta, post_scale;
+  int tiles_m, tiles_n, tiles_per_batch, total_tiles;
+  // Shared-memory descriptor geometry (bytes), filled in by the host:
+  //   adv_*: start-address advance per MMA instruction (32 bytes of K)
+  //   lbo_*/sbo_*: leading / stride byte offsets of the operand's canonical 128B-swizzled layout
+  unsigned int adv_a, adv_b, lbo_a, lbo_b, sbo_a, sbo_b;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
+  b = t / p.tiles_per_batch;
+  int r = t - b * p.tiles_per_batch;
+  if (p.tri) {
+    const int ratio = p.bn / kBlockM;
+    tj = 0;
+    ti = 0;
+    for (int j = 0; j < p.tiles_n; ++j) {
+      const int first = j * ratio;
+      const int cnt = p.tiles_m - first;
+      if (r < cnt) {
+        tj = j;
+        ti = first + r;
+        return;
+      }
+      r -= cnt;
+    }
+  } else {
+    const int per_group = kGroupM * p.tiles_n;
+    const int g = r / per_group;
+    const int first = g * kGroupM;
+    const int rows = min(kGroupM, p.tiles_m - first);
+    const int w = r - g * per_group;
+    ti = first + (w % rows);
+    tj = w / rows;
+  }
+}
+
+__device__ __forceinline__ void report(const GemmParams& p, unsigned int code) {
+  if (p.status != nullptr) atomicCAS(p.status, 0u, code);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short h) {
+  return __uint_as_float(static_cast<unsigned int>(h) << 16);
+}
+
+// Epilogue for one 32-column chunk held by one thread (row `row`, columns col0..col0+31).
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], long long batch_c,
+                                               long long batch_d, int row, int col0) {
+  if (row >= p.M) return;
+  const bool has_c = (p.beta != 0.0f) && (p.C != nullptr);
+  const int ncols = min(32, p.N - col0);
+  if (ncols <= 0) return;
+  // Number of leading columns this thread stores directly: all of them, or those with col <= row.
+  const int ndirect = p.tri ? max(0, min(ncols, row - col0 + 1)) : ncols;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(acc[j]);
+
+  const bool full = (ndirect == 32);
+  if (has_c) {
+    if (p.c_fp32) {
+      const float* c = reinterpret_cast<const float*>(p.C) + batch_c + static_cast<long long>(row) * p.ldc + col0;
+      if (full && p.vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(c) + q);
+          v[4 * q + 0] = fmaf(p.beta, t.x, v[4 * q + 0]);
+          v[4 * q + 1] = fmaf(p.beta, t.y, v[4 * q + 1]);
+          v[4 * q + 2] = fmaf(p.beta, t.z, v[4 * q + 2]);
+          v[4 * q + 3] = fmaf(p.beta, t.w, v[4 * q + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ndirect) v[j] = fmaf(p.beta, c[j], v[j]);
+      }
+    } else {
+      const unsigned short* c =
+          reinterpret_cast<const unsigned short*>(p.C) + batch_c + static_cast<long long>(row) * p.ldc + col0;
+      if (full && p.vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 t = __ldg(reinterpret_cast<const uint4*>(c) + q);
+          const unsigned int w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[8 * q + 2 * e + 0] = fmaf(p.beta, __uint_as_float(w[e] << 16), v[8 * q + 2 * e + 0]);
+            v[8 * q + 2 * e + 1] = fmaf(p.beta, __uint_as_float(w[e] & 0xFFFF0000u), v[8 * q + 2 * e + 1]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ndirect) v[j] = fmaf(p.beta, bf16_bits_to_float(c[j]), v[j]);
+      }
+    }
+  }
+
+  if (p.d_fp32) {
+    if (p.round_bf16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __bfloat162float(__float2bfloat16_rn(v[j])) * p.post_scale;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= p.post_scale;
+    }
+    float* d = reinterpret_cast<float*>(p.D) + batch_d;
+    float* drow = d + static_cast<long long>(row) * p.ldd + col0;
+    if (full && p.vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        reinterpret_cast<float4*>(drow)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ndirect) drow[j] = v[j];
+    }
+    if (p.tri && !p.skip_upper) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols && col0 + j < row) d[static_cast<long long>(col0 + j) * p.ldd + row] = v[j];
+    }
+  } else {
+    unsigned short h[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) h[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
+    unsigned short* d = reinterpret_cast<unsigned short*>(p.D) + batch_d;
+    unsigned short* drow = d + static_cast<long long>(row) * p.ldd + col0;
+    if (full && p.vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 t;
+        t.x = static_cast<unsigned int>(h[8 * q + 0]) | (static_cast<unsigned int>(h[8 * q + 1]) << 16);
+        t.y = static_cast<unsigned int>(h[8 * q + 2]) | (static_cast<unsigned int>(h[8 * q + 3]) << 16);
+        t.z = static_cast<unsigned int>(h[8 * q + 4]) | (static_cast<unsigned int>(h[8 * q + 5]) << 16);
+        t.w = static_cast<unsigned int>(h[8 * q + 6]) | (static_cast<unsigned int>(h[8 * q + 7]) << 16);
+        reinterpret_cast<uint4*>(drow)[q] = t;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ndirect) drow[j] = h[j];
+    }
+    if (p.tri && !p.skip_upper) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols && col0 + j < row) d[static_cast<long long>(col0 + j) * p.ldd + row] = h[j];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    eo_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle atoms are 1024 bytes: align the ring so that descriptor arithmetic holds.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;                     // [kStages]
+  uint64_t* empty_bar = bars + kStages;          // [kStages]
+  uint64_t* acc_full_bar = bars + 2 * kStages;   // [2]
+  uint64_t* acc_empty_bar = acc_full_bar + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], 4);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // Elements per 128-byte row and K extent of one pipeline stage / one MMA instruction.
+  const int bk = p.tf32 ? 32 : 64;
+  const int num_kb = (p.K + bk - 1) / bk;
+  const uint32_t stage_tx = static_cast<uint32_t>(kStageABytes + p.bn * kRowBytes);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        int b, ti, tj;
+        decode_tile(p, t, b, ti, tj);
+        const int m0 = ti * kBlockM;
+        const int n0 = tj * p.bn;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+            report(p, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kStageABytes;
+          mbar_expect_tx(&full_bar[stage], stage_tx);
+          const int k0 = kb * bk;
+          if (!p.a_mn) {
+            tma_load_3d(sa, &tmA, &full_bar[stage], k0, m0, b);  // box {bk, 128, 1}
+          } else {
+            // box {bk (M), bk (K), 1}: one 128-byte-wide M atom per copy
+            for (int q = 0; q < kBlockM / bk; ++q)
+              tma_load_3d(sa + q * bk * kRowBytes, &tmA, &full_bar[stage], m0 + q * bk, k0, b);
+          }
+          if (!p.b_mn) {
+            for (int q = 0; q < p.bn / kBlockM; ++q)
+              tma_load_3d(sb + q * kStageABytes, &tmB, &full_bar[stage], k0, n0 + q * kBlockM, b);
+          } else {
+            for (int q = 0; q < p.bn / bk; ++q)
+              tma_load_3d(sb + q * bk * kRowBytes, &tmB, &full_bar[stage], n0 + q * bk, k0, b);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(p.tf32 ? 2u : 1u, p.a_mn != 0, p.b_mn != 0, kBlockM, p.bn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int ab = 0;
+      uint32_t aphase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+          report(p, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            report(p, kStatusTimeoutMma + 1u);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kStageABytes;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * p.adv_a, p.lbo_a, p.sbo_a);
+            const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
+            if (p.tf32)
+              umma_tf32(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full_bar[ab]);
+        if (++ab == 2) {
+          ab = 0;
+          aphase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int ab = 0;
+    uint32_t aphase = 0;
+    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+      int b, ti, tj;
+      decode_tile(p, t, b, ti, tj);
+      const int m0 = ti * kBlockM;
+      const int n0 = tj * p.bn;
+      if (!mbar_wait(&acc_full_bar[ab], aphase)) {
+        report(p, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const int warp_last_row = m0 + quarter * 32 + 31;
+      const long long batch_c = static_cast<long long>(b) * p.strideC;
+      const long long batch_d = static_cast<long long>(b) * p.strideD;
+      const int nchunks = p.bn / 32;
+      for (int c = 0; c < nchunks; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        if (p.tri && col0 > warp_last_row) break;  // whole chunk lies above the diagonal for this warp
+        uint32_t acc[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                          static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
+                      acc);
+        tmem_ld_wait();
+        epilogue_chunk(p, acc, batch_c, batch_d, row, col0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[ab]);
+      if (++ab == 2) {
+        ab = 0;
+        aphase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace eo

@@ -1,0 +1,131 @@
+/*
+ * C ABI of libeo_b200.so: hand-written sm_100a kernels for the Newton-Schulz orthogonalization
+ * path of the Muon / OrthogonalizedOptimizer step.
+ *
+ * Conventions shared by every entry point:
+ *   - plain pointers and sizes only; device pointers unless a name says `host_`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); work is only
+ *     enqueued, nothing synchronises the stream;
+ *   - the return value is an eo_status; on failure eo_last_error() describes it (thread-local);
+ *   - matrices are row-major with a leading dimension `ld*` counted in elements and a batch
+ *     stride counted in elements; bf16 operands must have 16-byte-aligned base pointers and
+ *     ld / stride multiples of 8 elements (fp32: 4), which is what a TMA descriptor needs;
+ *   - no entry point allocates or frees device memory: callers own inputs, outputs and scratch.
+ *
+ * Citations name the file:line of the reference (NVIDIA-NeMo/Emerging-Optimizers) call site that
+ * an entry point stands in for.
+ */
+#ifndef EO_B200_H_
+#define EO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum eo_status {
+  EO_OK = 0,
+  EO_ERR_BAD_ARG = 1,       /* shape / alignment / flag rejected before any launch */
+  EO_ERR_CUDA = 2,          /* a CUDA runtime or driver call failed */
+  EO_ERR_UNSUPPORTED = 3,   /* device is not compute capability 10.x */
+  EO_ERR_WORKSPACE = 4,     /* scratch buffer too small */
+  EO_ERR_DEVICE_WAIT = 5    /* a bounded wait inside a kernel ran out (see eo_read_device_status) */
+} eo_status;
+
+/* Library / build identification: "eo_b200 <version> sm_100a". */
+const char* eo_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* eo_last_error(void);
+
+/*
+ * Reads and clears the status word that kernels of this library write when one of their bounded
+ * waits (mbarrier, accumulator hand-off, peer flag) runs out.  Synchronises `stream` first.
+ * *host_code receives 0 when every kernel completed normally.
+ */
+int eo_read_device_status(uint32_t* host_code, void* stream);
+
+/*
+ * General tensor-core product with a fused affine epilogue, fp32 accumulation:
+ *
+ *     D[b] = alpha * op(A[b]) * op(B[b])^T + beta * C[b],     b = 0 .. batch-1
+ *
+ * op(A) is M x K and op(B) is N x K.  `a_mn_major == 0`: A is stored M x K row-major (K
+ * contiguous, leading dimension lda); `a_mn_major == 1`: A is stored K x M row-major (M
+ * contiguous).  Same for B with N.  C and D are M x N row-major.
+ *
+ * `precision`: 0 = bf16 operands (A, B, C bf16); 1 = fp32 operands read as tf32 (A, B, C fp32).
+ * `d_fp32`   : D is fp32 (1) or bf16 (0; only with precision 0).
+ * `round_bf16`: with d_fp32, round alpha*acc + beta*C to bf16 first, then widen and multiply by
+ *               post_scale (keeps the rounding point of a bf16 kernel followed by `.to(float32) * s`).
+ * C may be NULL when beta == 0.
+ *
+ * Stands in for torch.addmm / torch.baddbmm at
+ * emerging_optimizers/orthogonalized_optimizers/muon_utils.py:374-377, 407-410, 439-441, 473-475,
+ * and for the trailing `.to(torch.float32)` (:269) and scale multiply
+ * (emerging_optimizers/orthogonalized_optimizers/muon.py:132) when d_fp32 is set.
+ */
+int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA,
+            const void* B, int b_mn_major, int64_t ldb, int64_t strideB,
+            const void* C, int64_t ldc, int64_t strideC,
+            void* D, int64_t ldd, int64_t strideD,
+            int batch, int M, int N, int K,
+            float alpha, float beta, float post_scale,
+            int precision, int d_fp32, int round_bf16, void* stream);
+
+/*
+ * Symmetric rank-k update, lower triangle computed and mirrored:
+ *
+ *     D[b] = alpha * A[b] * A[b]^T + beta * C[b],     A[b] is N x K,  C[b], D[b] are N x N
+ *
+ * `a_trans == 0`: A stored N x K row-major; `a_trans == 1`: A stored K x N row-major (i.e. the
+ * caller's A is a transposed view of a contiguous K x N array).  C must be symmetric; only its
+ * lower triangle is read.  `skip_upper != 0` leaves the strict upper triangle of D untouched.
+ * `precision` as in eo_gemm (0: bf16 in/out; 1: fp32 in/out through tf32).
+ *
+ * Stands in for tsyrk_ex / tsyrk_ex_small_matrix (emerging_optimizers/triton_kernels/syrk.py:335-500)
+ * and batched_tsyrk_ex (emerging_optimizers/triton_kernels/batched_syrk.py:266-363).
+ */
+int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA,
+            const void* C, int64_t ldc, int64_t strideC,
+            void* D, int64_t ldd, int64_t strideD,
+            int batch, int N, int K, float alpha, float beta, int skip_upper,
+            int precision, void* stream);
+
+/*
+ * Bytes of scratch eo_sumsq_f32 needs for `batch` matrices of rows x cols.
+ */
+size_t eo_sumsq_scratch_bytes(int batch, int64_t rows, int64_t cols);
+
+/*
+ * sumsq[b] = sum over the rows x cols fp32 matrix b of x^2, accumulated in float64 in a fixed
+ * order (run-to-run deterministic).  `sumsq` is double[batch] on the device; `scratch` must hold
+ * eo_sumsq_scratch_bytes(...) bytes.
+ *
+ * First half of torch.nn.functional.normalize / torch.linalg.vector_norm at
+ * emerging_optimizers/orthogonalized_optimizers/muon_utils.py:216, 221 and of
+ * distributed_normalize_p2 (:140-141); a tensor-parallel caller all-reduces `sumsq` between this
+ * call and eo_normalize_f32.
+ */
+int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                 double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * out[b] = x[b] / denom[b],  denom[b] = (float)sqrt(sumsq[b]), clamped from below by eps when
+ * `clamp_eps` is set.  Output is bf16 (out_fp32 == 0) or fp32; with out_fp32 and round_bf16 the
+ * quotient is rounded to bf16 and widened again.
+ *
+ * Second half of the normalisation at muon_utils.py:143-146, 216, 222 fused with the bf16
+ * down-cast at :262.
+ */
+int eo_normalize_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                     const double* sumsq, float eps, int clamp_eps,
+                     void* out, int64_t ldo, int64_t strideo, int out_fp32, int round_bf16, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* EO_B200_H_ */
