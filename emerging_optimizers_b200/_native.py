@@ -32,8 +32,8 @@ _PROTOTYPES: dict[str, tuple] = {
     "eo_read_device_status": (c_int, [POINTER(c_uint32), c_void_p]),
     "eo_gemm": (
         c_int,
-        [c_void_p, c_int, c_int64, c_int64]
-        + [c_void_p, c_int, c_int64, c_int64]
+        [c_void_p, c_int, c_int64, c_int64, c_int64]
+        + [c_void_p, c_int, c_int64, c_int64, c_int64]
         + [c_void_p, c_int64, c_int64]
         + [c_void_p, c_int64, c_int64]
         + [c_int, c_int, c_int, c_int]
@@ -42,10 +42,14 @@ _PROTOTYPES: dict[str, tuple] = {
     ),
     "eo_syrk": (
         c_int,
-        [c_void_p, c_int, c_int64, c_int64]
+        [c_void_p, c_int, c_int64, c_int64, c_int64]
         + [c_void_p, c_int64, c_int64]
         + [c_void_p, c_int64, c_int64]
         + [c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
+    ),
+    "eo_split_f32": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_void_p],
     ),
     "eo_sumsq_scratch_bytes": (c_size_t, [c_int, c_int64, c_int64]),
     "eo_sumsq_f32": (
@@ -120,21 +124,84 @@ def read_device_status(device: torch.device | None = None) -> int:
 
 
 def _mat_layout(t: torch.Tensor) -> tuple[int, int, int]:
-    """(mn_major, ld, batch_stride) of a 2-D/3-D tensor whose last two dims are row- or column-major."""
+    """(mn_major, ld, batch_stride) of a 2-D/3-D tensor whose last two dims are row- or column-major.
+
+    ``mn_major == 0``: the last dim is contiguous (row-major, ``ld`` = row stride);
+    ``mn_major == 1``: the second-to-last dim is contiguous (a transposed view, ``ld`` = column stride).
+    """
+    rows, cols = t.size(-2), t.size(-1)
     s1, s2 = t.stride(-2), t.stride(-1)
     bs = t.stride(0) if t.dim() == 3 else 0
-    if s2 == 1 or t.size(-1) == 1:
-        if t.size(-1) == 1 and s2 != 1:
-            return 0, max(s1, 1), bs
-        return 0, s1 if t.size(-2) > 1 else max(s1, t.size(-1)), bs
-    if s1 == 1:
-        return 1, s2 if t.size(-1) > 1 else max(s2, t.size(-2)), bs
+    if (s2 == 1 or cols == 1) and (s1 >= cols or rows == 1):
+        return 0, (s1 if rows > 1 else cols), bs
+    if (s1 == 1 or rows == 1) and (s2 >= rows or cols == 1):
+        return 1, (s2 if cols > 1 else rows), bs
     raise NativeLibraryError(f"unsupported strides {t.stride()} for shape {tuple(t.shape)}")
 
 
+def is_matrix_layout(t: torch.Tensor) -> bool:
+    """True when the last two dims of ``t`` are row- or column-major (what the kernels can address)."""
+    try:
+        _mat_layout(t)
+    except NativeLibraryError:
+        return False
+    return True
+
+
+class Split3:
+    """An fp32 matrix (batch) stored as three bf16 planes whose sum reproduces it to about 2^-24 relative.
+
+    ``planes`` has shape (3, [B,] R, C) in the physical (row-major) orientation of the source; ``mn`` records
+    whether the logical matrix is the transpose of that storage.  See ``eo_split_f32``.
+    """
+
+    def __init__(self, x: torch.Tensor):
+        require_cuda(x, "x")
+        assert x.dtype == torch.float32
+        mn, ld, bs = _mat_layout(x)
+        rows, cols = (x.size(-2), x.size(-1)) if mn == 0 else (x.size(-1), x.size(-2))
+        batch = x.size(0) if x.dim() == 3 else 1
+        ldo = (cols + 7) // 8 * 8
+        mat = rows * ldo
+        self.planes = torch.empty((3, batch, mat), dtype=torch.bfloat16, device=x.device)
+        self.mn, self.ld, self.bstride, self.plane_stride = mn, ldo, mat, batch * mat
+        self.shape, self.batch, self.device = tuple(x.shape), batch, x.device
+        with torch.cuda.device(x.device):
+            rc = lib().eo_split_f32(
+                x.data_ptr(), batch, rows, cols, ld, bs, self.planes.data_ptr(), ldo, mat, self.plane_stride, _stream(x)
+            )
+        _check(rc, "eo_split_f32")
+
+    @property
+    def mT(self) -> "Split3":
+        """The transposed matrix: same planes, opposite orientation flag."""
+        t = object.__new__(Split3)
+        t.__dict__.update(self.__dict__)
+        t.mn = 1 - self.mn
+        t.shape = (*self.shape[:-2], self.shape[-1], self.shape[-2])
+        return t
+
+    def data_ptr(self) -> int:
+        return self.planes.data_ptr()
+
+    def size(self, d: int) -> int:
+        return self.shape[d]
+
+    def dim(self) -> int:
+        return len(self.shape)
+
+
+def _operand(t: "torch.Tensor | Split3") -> tuple[int, int, int, int, int]:
+    """(pointer, mn_major, ld, batch_stride, plane_stride) of a bf16 tensor or a split fp32 operand."""
+    if isinstance(t, Split3):
+        return t.data_ptr(), t.mn, t.ld, t.bstride, t.plane_stride
+    mn, ld, bs = _mat_layout(t)
+    return t.data_ptr(), mn, ld, bs, 0
+
+
 def gemm(
-    a: torch.Tensor,
-    b: torch.Tensor,
+    a: "torch.Tensor | Split3",
+    b: "torch.Tensor | Split3",
     c: torch.Tensor | None,
     out: torch.Tensor,
     alpha: float = 1.0,
@@ -144,40 +211,45 @@ def gemm(
 ) -> torch.Tensor:
     """``out = alpha * a @ b + beta * c`` with ``a`` (.., M, K), ``b`` (.., K, N); see ``eo_gemm``.
 
-    ``a`` and ``b`` may be row- or column-major in their last two dims; ``c`` and ``out`` row-major.
+    bf16 tensors run the plain bf16 product; :class:`Split3` operands (both) run the fp32-accurate product with
+    fp32 ``c`` / ``out``.  ``a`` and ``b`` may be row- or column-major; ``c`` and ``out`` row-major.
     """
-    require_cuda(a, "a")
     batch = a.size(0) if a.dim() == 3 else 1
     M, K = a.size(-2), a.size(-1)
     N = b.size(-1)
     assert b.size(-2) == K and out.size(-2) == M and out.size(-1) == N
-    precision = 0 if a.dtype == torch.bfloat16 else 1
+    split = isinstance(a, Split3)
+    assert split == isinstance(b, Split3), "both operands must be split, or neither"
+    if not split:
+        require_cuda(a, "a")
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     # The kernel takes op(B) as N x K: b (K x N row-major) is "MN-major", b column-major is "K-major".
-    a_mn, lda, sa = _mat_layout(a)
-    bt_mn, ldb, sb = _mat_layout(b.mT)
+    pa, a_mn, lda, sa, pla = _operand(a)
+    pb, bt_mn, ldb, sb, plb = _operand(b.mT)
     if c is not None:
         c_mn, ldc, sc = _mat_layout(c)
         assert c_mn == 0, "c must be row-major"
+        assert c.dtype == (torch.float32 if split else torch.bfloat16)
     else:
         ldc, sc = 0, 0
     d_mn, ldd, sd = _mat_layout(out)
     assert d_mn == 0, "out must be row-major"
-    with torch.cuda.device(a.device):
+    with torch.cuda.device(out.device):
         rc = lib().eo_gemm(
-            a.data_ptr(), a_mn, lda, sa,
-            b.data_ptr(), bt_mn, ldb, sb,
+            pa, a_mn, lda, sa, pla,
+            pb, bt_mn, ldb, sb, plb,
             c.data_ptr() if c is not None else None, ldc, sc,
             out.data_ptr(), ldd, sd,
             batch, M, N, K,
             alpha, beta, post_scale,
-            precision, 1 if out.dtype == torch.float32 else 0, 1 if round_bf16 else 0, _stream(a),
+            1 if split else 0, 1 if out.dtype == torch.float32 else 0, 1 if round_bf16 else 0, _stream(out),
         )  # fmt: skip
     _check(rc, "eo_gemm")
     return out
 
 
 def syrk(
-    a: torch.Tensor,
+    a: "torch.Tensor | Split3",
     c: torch.Tensor | None,
     out: torch.Tensor,
     alpha: float = 1.0,
@@ -185,11 +257,12 @@ def syrk(
     skip_upper: bool = False,
 ) -> torch.Tensor:
     """``out = alpha * a @ a.mT + beta * c`` (lower triangle computed, mirrored); see ``eo_syrk``."""
-    require_cuda(a, "a")
+    split = isinstance(a, Split3)
+    if not split:
+        require_cuda(a, "a")
     batch = a.size(0) if a.dim() == 3 else 1
     N, K = a.size(-2), a.size(-1)
-    precision = 0 if a.dtype == torch.bfloat16 else 1
-    a_mn, lda, sa = _mat_layout(a)
+    pa, a_mn, lda, sa, pla = _operand(a)
     if c is not None:
         # c is symmetric: a column-major c is read as its own transpose.
         _, ldc, sc = _mat_layout(c)
@@ -197,12 +270,13 @@ def syrk(
         ldc, sc = 0, 0
     d_mn, ldd, sd = _mat_layout(out)
     assert d_mn == 0, "out must be row-major"
-    with torch.cuda.device(a.device):
+    assert out.dtype == (torch.float32 if split else torch.bfloat16)
+    with torch.cuda.device(out.device):
         rc = lib().eo_syrk(
-            a.data_ptr(), a_mn, lda, sa,
+            pa, a_mn, lda, sa, pla,
             c.data_ptr() if c is not None else None, ldc, sc,
             out.data_ptr(), ldd, sd,
-            batch, N, K, alpha, beta, 1 if skip_upper else 0, precision, _stream(a),
+            batch, N, K, alpha, beta, 1 if skip_upper else 0, 1 if split else 0, _stream(out),
         )  # fmt: skip
     _check(rc, "eo_syrk")
     return out

@@ -124,6 +124,46 @@ __global__ void __launch_bounds__(kEwThreads)
   }
 }
 
+// Split fp32 into three bf16 planes with x = p0 + p1 + p2 up to 2^-24 relative: p0 = bf16(x),
+// p1 = bf16(x - p0), p2 = bf16(x - p0 - p1); both remainders are exact in fp32.
+__global__ void __launch_bounds__(kEwThreads)
+    split3_kernel(const float* __restrict__ x, long long rows, long long cols, long long ld, long long stride,
+                  __nv_bfloat16* __restrict__ out, long long ldo, long long strideo, long long plane_stride) {
+  const int b = blockIdx.y;
+  const float* xb = x + static_cast<long long>(b) * stride;
+  __nv_bfloat16* ob = out + static_cast<long long>(b) * strideo;
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  const long long units = rows * cols;
+  for (long long u = tid; u < units; u += nthreads) {
+    const long long r = u / cols, c = u - r * cols;
+    const float v = xb[r * ld + c];
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h0);
+    const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(h1);
+    const __nv_bfloat16 h2 = __float2bfloat16_rn(r2);
+    const long long o = r * ldo + c;
+    ob[o] = h0;
+    ob[o + plane_stride] = h1;
+    ob[o + 2 * plane_stride] = h2;
+  }
+}
+
+inline void launch_split3(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                          void* out, int64_t ldo, int64_t strideo, int64_t plane_stride, cudaStream_t stream) {
+  const long long total = static_cast<long long>(rows) * cols;
+  long long nblk = (total + kEwThreads * 4 - 1) / (kEwThreads * 4);
+  if (nblk < 1) nblk = 1;
+  if (nblk > 4096) nblk = 4096;
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    const int nb = (batch - b0 < 65535) ? (batch - b0) : 65535;
+    split3_kernel<<<dim3(static_cast<unsigned>(nblk), nb), kEwThreads, 0, stream>>>(
+        x + static_cast<long long>(b0) * stride, rows, cols, ld, stride,
+        static_cast<__nv_bfloat16*>(out) + static_cast<long long>(b0) * strideo, ldo, strideo, plane_stride);
+  }
+}
+
 inline void launch_sumsq(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
                          double* sumsq, double* scratch, cudaStream_t stream) {
   const int nblk = sumsq_blocks_per_matrix(rows, cols);

@@ -99,15 +99,17 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
   return EO_OK;
 }
 
-int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, const void* B, int b_mn, int64_t ldb,
-                int64_t strideB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
+int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t planeA, const void* B, int b_mn,
+                int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
                 int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
                 int round_bf16, int tri, int skip_upper, void* stream) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(EO_ERR_BAD_ARG, "negative size");
-  if (precision != 0 && precision != 1) return fail(EO_ERR_BAD_ARG, "precision must be 0 (bf16) or 1 (tf32)");
-  if (precision == 1 && !d_fp32) return fail(EO_ERR_BAD_ARG, "tf32 precision needs an fp32 output");
+  if (precision != 0 && precision != 1) return fail(EO_ERR_BAD_ARG, "precision must be 0 (bf16) or 1 (split fp32)");
+  if (precision == 1 && !d_fp32) return fail(EO_ERR_BAD_ARG, "split-fp32 precision needs an fp32 output");
+  if (precision == 1 && (planeA % 8 != 0 || planeB % 8 != 0 || planeA <= 0 || planeB <= 0))
+    return fail(EO_ERR_BAD_ARG, "plane strides must be positive multiples of 8 elements");
   if (beta != 0.0f && C == nullptr) return fail(EO_ERR_BAD_ARG, "beta != 0 needs C");
   if (A == nullptr || B == nullptr || D == nullptr) {
     if (batch == 0 || M == 0 || N == 0) return EO_OK;
@@ -116,20 +118,26 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, const voi
   if (batch == 0 || M == 0 || N == 0) return EO_OK;
   if (K == 0) return fail(EO_ERR_BAD_ARG, "K == 0 is not supported");
 
-  const int eb = precision == 0 ? 2 : 4;
-  const int bk = eo::kRowBytes / eb;
-  CUtensorMap tmA, tmB;
-  int rc;
-  if (!a_mn)
-    rc = make_map(&tmA, A, eb, K, M, batch, lda, strideA, bk, eo::kBlockM);
-  else
-    rc = make_map(&tmA, A, eb, M, K, batch, lda, strideA, bk, bk);
-  if (rc) return rc;
-  if (!b_mn)
-    rc = make_map(&tmB, B, eb, K, N, batch, ldb, strideB, bk, eo::kBlockM);
-  else
-    rc = make_map(&tmB, B, eb, N, K, batch, ldb, strideB, bk, bk);
-  if (rc) return rc;
+  const int eb = 2;  // operands are bf16 (plain) or bf16 planes (split fp32)
+  const int bk = eo::kBlockK;
+  const int nplanes = precision == 0 ? 1 : eo::kMaxPlanes;
+  eo::GemmMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int pl = 0; pl < nplanes; ++pl) {
+    const void* a_pl = static_cast<const char*>(A) + static_cast<int64_t>(pl) * planeA * eb;
+    const void* b_pl = static_cast<const char*>(B) + static_cast<int64_t>(pl) * planeB * eb;
+    int rc;
+    if (!a_mn)
+      rc = make_map(&maps.a[pl], a_pl, eb, K, M, batch, lda, strideA, bk, eo::kBlockM);
+    else
+      rc = make_map(&maps.a[pl], a_pl, eb, M, K, batch, lda, strideA, bk, bk);
+    if (rc) return rc;
+    if (!b_mn)
+      rc = make_map(&maps.b[pl], b_pl, eb, K, N, batch, ldb, strideB, bk, eo::kBlockM);
+    else
+      rc = make_map(&maps.b[pl], b_pl, eb, N, K, batch, ldb, strideB, bk, bk);
+    if (rc) return rc;
+  }
 
   eo::GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -139,7 +147,19 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, const voi
   p.K = K;
   p.a_mn = a_mn;
   p.b_mn = b_mn;
-  p.tf32 = precision;
+  if (precision == 0) {
+    p.nterms = 1;
+  } else {
+    // x = x0 + x1 + x2: keep every product of planes i, j with i + j <= 2, smallest contributions first so
+    // that they are not absorbed by the large one in the fp32 accumulator.
+    static const int ta[6] = {0, 2, 1, 0, 1, 0};
+    static const int tb[6] = {2, 0, 1, 1, 0, 0};
+    p.nterms = 6;
+    for (int t = 0; t < 6; ++t) {
+      p.term_a[t] = ta[t];
+      p.term_b[t] = tb[t];
+    }
+  }
   p.tri = tri;
   p.skip_upper = skip_upper;
   p.c_fp32 = precision;
@@ -205,7 +225,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, const voi
   p.tiles_per_batch = p.total_tiles / batch;
 
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-  eo::eo_gemm_kernel<<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmA, tmB, p);
+  eo::eo_gemm_kernel<<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }
@@ -235,21 +255,35 @@ int eo_read_device_status(uint32_t* host_code, void* stream) {
   return EO_OK;
 }
 
-int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA, const void* B, int b_mn_major, int64_t ldb,
-            int64_t strideB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
-            int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
-            int round_bf16, void* stream) {
-  return launch_gemm(A, a_mn_major, lda, strideA, B, b_mn_major, ldb, strideB, C, ldc, strideC, D, ldd, strideD, batch,
+int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA, int64_t planeA, const void* B,
+            int b_mn_major, int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC,
+            void* D, int64_t ldd, int64_t strideD, int batch, int M, int N, int K, float alpha, float beta,
+            float post_scale, int precision, int d_fp32, int round_bf16, void* stream) {
+  return launch_gemm(A, a_mn_major, lda, strideA, planeA, B, b_mn_major, ldb, strideB, planeB, C, ldc, strideC, D, ldd, strideD, batch,
                      M, N, K, alpha, beta, post_scale, precision, d_fp32, round_bf16, /*tri=*/0, /*skip_upper=*/0,
                      stream);
 }
 
-int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA, const void* C, int64_t ldc, int64_t strideC,
-            void* D, int64_t ldd, int64_t strideD, int batch, int N, int K, float alpha, float beta, int skip_upper,
-            int precision, void* stream) {
-  return launch_gemm(A, a_trans, lda, strideA, A, a_trans, lda, strideA, C, ldc, strideC, D, ldd, strideD, batch, N, N,
+int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA, int64_t planeA, const void* C, int64_t ldc,
+            int64_t strideC, void* D, int64_t ldd, int64_t strideD, int batch, int N, int K, float alpha, float beta,
+            int skip_upper, int precision, void* stream) {
+  return launch_gemm(A, a_trans, lda, strideA, planeA, A, a_trans, lda, strideA, planeA, C, ldc, strideC, D, ldd, strideD, batch, N, N,
                      K, alpha, beta, 1.0f, precision, /*d_fp32=*/precision, /*round_bf16=*/0, /*tri=*/1, skip_upper,
                      stream);
+}
+
+int eo_split_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride, void* planes,
+                 int64_t ldo, int64_t strideo, int64_t plane_stride, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (batch == 0 || rows == 0 || cols == 0) return EO_OK;
+  if (x == nullptr || planes == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (ld < cols || ldo < cols) return fail(EO_ERR_BAD_ARG, "leading dimension smaller than cols");
+  eo::launch_split3(x, batch, rows, cols, ld, stride, planes, ldo, strideo, plane_stride,
+                    static_cast<cudaStream_t>(stream));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
 }
 
 size_t eo_sumsq_scratch_bytes(int batch, int64_t rows, int64_t cols) {

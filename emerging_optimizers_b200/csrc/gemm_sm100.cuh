@@ -24,7 +24,9 @@ namespace eo {
 
 constexpr int kBlockM = 128;
 constexpr int kMaxBlockN = 256;
-constexpr int kRowBytes = 128;  // one swizzle row: 64 bf16 or 32 fp32 along the contiguous dimension
+constexpr int kRowBytes = 128;  // one swizzle row: 64 bf16 along the contiguous dimension
+constexpr int kBlockK = 64;     // K extent of one pipeline stage
+constexpr int kMaxPlanes = 3;   // bf16 planes of a split-fp32 operand
 constexpr int kStages = 4;
 constexpr int kStageABytes = kBlockM * kRowBytes;     // 16 KiB
 constexpr int kStageBBytes = kMaxBlockN * kRowBytes;  // 32 KiB
@@ -40,7 +42,9 @@ struct GemmParams {
   int batch, M, N, K;
   int bn;          // tile width: 128 or 256
   int a_mn, b_mn;  // operand stored MN-major (1) or K-major (0)
-  int tf32;        // 0: bf16 operands (kind::f16); 1: fp32 storage read as tf32 (kind::tf32)
+  int nterms;      // operand-plane pairs accumulated into one result (1: plain bf16; 6: split-fp32 product)
+  int term_a[6];   // plane of A used by term t
+  int term_b[6];   // plane of B used by term t
   int tri;         // symmetric update: lower-triangle tiles only
   int skip_upper;  // with tri: do not mirror into the upper triangle
   int c_fp32;      // element type of C: fp32 (1) or bf16 (0)
@@ -202,9 +206,16 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+// TMA descriptors of up to three bf16 planes per operand.  A plain bf16 product uses plane 0 only; an
+// fp32-accurate product stores each fp32 operand as x = p0 + p1 + p2 (three bf16 roundings of the running
+// remainder) and accumulates the six largest plane products into the same fp32 accumulator.
+struct GemmMaps {
+  CUtensorMap a[kMaxPlanes];
+  CUtensorMap b[kMaxPlanes];
+};
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
-    eo_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                   const GemmParams p) {
+    eo_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the ring so that descriptor arithmetic holds.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -228,8 +239,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(&acc_empty_bar[s], 4);
     }
     mbar_init_fence();
-    tma_prefetch_desc(&tmA);
-    tma_prefetch_desc(&tmB);
+    for (int t = 0; t < p.nterms; ++t) {
+      tma_prefetch_desc(&maps.a[p.term_a[t]]);
+      tma_prefetch_desc(&maps.b[p.term_b[t]]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -240,9 +253,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Elements per 128-byte row and K extent of one pipeline stage / one MMA instruction.
-  const int bk = p.tf32 ? 32 : 64;
+  constexpr int bk = kBlockK;
   const int num_kb = (p.K + bk - 1) / bk;
+  const int num_it = num_kb * p.nterms;  // pipeline iterations per tile
   const uint32_t stage_tx = static_cast<uint32_t>(kStageABytes + p.bn * kRowBytes);
 
   if (warp == 0) {
@@ -256,7 +269,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         decode_tile(p, t, b, ti, tj);
         const int m0 = ti * kBlockM;
         const int n0 = tj * p.bn;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int term = 0, kb = 0;
+        for (int it = 0; it < num_it; ++it) {
+          const CUtensorMap* tmA = &maps.a[p.term_a[term]];
+          const CUtensorMap* tmB = &maps.b[p.term_b[term]];
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report(p, kStatusTimeoutProducer);
             ok = false;
@@ -267,22 +283,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           mbar_expect_tx(&full_bar[stage], stage_tx);
           const int k0 = kb * bk;
           if (!p.a_mn) {
-            tma_load_3d(sa, &tmA, &full_bar[stage], k0, m0, b);  // box {bk, 128, 1}
+            tma_load_3d(sa, tmA, &full_bar[stage], k0, m0, b);  // box {bk, 128, 1}
           } else {
             // box {bk (M), bk (K), 1}: one 128-byte-wide M atom per copy
             for (int q = 0; q < kBlockM / bk; ++q)
-              tma_load_3d(sa + q * bk * kRowBytes, &tmA, &full_bar[stage], m0 + q * bk, k0, b);
+              tma_load_3d(sa + q * bk * kRowBytes, tmA, &full_bar[stage], m0 + q * bk, k0, b);
           }
           if (!p.b_mn) {
             for (int q = 0; q < p.bn / kBlockM; ++q)
-              tma_load_3d(sb + q * kStageABytes, &tmB, &full_bar[stage], k0, n0 + q * kBlockM, b);
+              tma_load_3d(sb + q * kStageABytes, tmB, &full_bar[stage], k0, n0 + q * kBlockM, b);
           } else {
             for (int q = 0; q < p.bn / bk; ++q)
-              tma_load_3d(sb + q * bk * kRowBytes, &tmB, &full_bar[stage], n0 + q * bk, k0, b);
+              tma_load_3d(sb + q * bk * kRowBytes, tmB, &full_bar[stage], n0 + q * bk, k0, b);
           }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
+          }
+          if (++kb == num_kb) {
+            kb = 0;
+            ++term;
           }
         }
       }
@@ -290,7 +310,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc(p.tf32 ? 2u : 1u, p.a_mn != 0, p.b_mn != 0, kBlockM, p.bn);
+      const uint32_t idesc = make_idesc(1u, p.a_mn != 0, p.b_mn != 0, kBlockM, p.bn);
       int stage = 0;
       uint32_t phase = 0;
       int ab = 0;
@@ -303,7 +323,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int it = 0; it < num_it; ++it) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             report(p, kStatusTimeoutMma + 1u);
             ok = false;
@@ -316,10 +336,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           for (int k = 0; k < 4; ++k) {
             const uint64_t da = make_smem_desc(sa + k * p.adv_a, p.lbo_a, p.sbo_a);
             const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
-            if (p.tf32)
-              umma_tf32(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-            else
-              umma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(tmem_d, da, db, idesc, (it | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == kStages) {

@@ -146,19 +146,6 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       : "memory");
 }
 
-// Same with kind::tf32 (fp32 storage, 10-bit mantissa operands, fp32 accumulation).
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 // Make `bar` complete once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -200,8 +187,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   return d;
 }
 
-// Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation.
-//   bits 4-5: D format (1 = f32)   bits 7-9: A format   bits 10-12: B format (f16 kind: 0 f16, 1 bf16; tf32 kind: 2)
+// Instruction descriptor for kind::f16 with fp32 accumulation.
+//   bits 4-5: D format (1 = f32)   bits 7-9: A format   bits 10-12: B format (0 f16, 1 bf16)
 //   bit 15: A is MN-major   bit 16: B is MN-major   bits 17-22: N >> 3   bits 24-28: M >> 4
 __device__ __forceinline__ uint32_t make_idesc(uint32_t ab_format, bool a_mn_major, bool b_mn_major, uint32_t m,
                                                uint32_t n) {

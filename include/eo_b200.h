@@ -56,7 +56,11 @@ int eo_read_device_status(uint32_t* host_code, void* stream);
  * contiguous, leading dimension lda); `a_mn_major == 1`: A is stored K x M row-major (M
  * contiguous).  Same for B with N.  C and D are M x N row-major.
  *
- * `precision`: 0 = bf16 operands (A, B, C bf16); 1 = fp32 operands read as tf32 (A, B, C fp32).
+ * `precision`: 0 = bf16 operands (A, B, C bf16; planeA / planeB ignored);
+ *              1 = fp32-accurate product of split operands: A and B each point to three bf16 planes
+ *                  (see eo_split_f32) `planeA` / `planeB` elements apart, all with the layout given by
+ *                  lda / strideA (ldb / strideB); the six plane products p_i * q_j with i + j <= 2 are
+ *                  accumulated in fp32.  C and D are fp32.
  * `d_fp32`   : D is fp32 (1) or bf16 (0; only with precision 0).
  * `round_bf16`: with d_fp32, round alpha*acc + beta*C to bf16 first, then widen and multiply by
  *               post_scale (keeps the rounding point of a bf16 kernel followed by `.to(float32) * s`).
@@ -67,8 +71,8 @@ int eo_read_device_status(uint32_t* host_code, void* stream);
  * and for the trailing `.to(torch.float32)` (:269) and scale multiply
  * (emerging_optimizers/orthogonalized_optimizers/muon.py:132) when d_fp32 is set.
  */
-int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA,
-            const void* B, int b_mn_major, int64_t ldb, int64_t strideB,
+int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA, int64_t planeA,
+            const void* B, int b_mn_major, int64_t ldb, int64_t strideB, int64_t planeB,
             const void* C, int64_t ldc, int64_t strideC,
             void* D, int64_t ldd, int64_t strideD,
             int batch, int M, int N, int K,
@@ -83,16 +87,27 @@ int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA,
  * `a_trans == 0`: A stored N x K row-major; `a_trans == 1`: A stored K x N row-major (i.e. the
  * caller's A is a transposed view of a contiguous K x N array).  C must be symmetric; only its
  * lower triangle is read.  `skip_upper != 0` leaves the strict upper triangle of D untouched.
- * `precision` as in eo_gemm (0: bf16 in/out; 1: fp32 in/out through tf32).
+ * `precision` as in eo_gemm (0: bf16 in/out; 1: A given as three bf16 planes `planeA` elements apart,
+ * C and D fp32).
  *
  * Stands in for tsyrk_ex / tsyrk_ex_small_matrix (emerging_optimizers/triton_kernels/syrk.py:335-500)
  * and batched_tsyrk_ex (emerging_optimizers/triton_kernels/batched_syrk.py:266-363).
  */
-int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA,
+int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA, int64_t planeA,
             const void* C, int64_t ldc, int64_t strideC,
             void* D, int64_t ldd, int64_t strideD,
             int batch, int N, int K, float alpha, float beta, int skip_upper,
             int precision, void* stream);
+
+/*
+ * Split an fp32 matrix batch into three bf16 planes with x = p0 + p1 + p2 (to 2^-24 relative):
+ * p0 = bf16(x), p1 = bf16(x - p0), p2 = bf16(x - p0 - p1).  Plane i is written at
+ * planes + i * plane_stride (elements), each with leading dimension ldo and batch stride strideo.
+ * Feeds the precision-1 mode of eo_gemm / eo_syrk, which stands in for the fp32 ("highest" / "high")
+ * matmuls of muon_utils.py:370-377 when torch.get_float32_matmul_precision() is not "medium" (:245).
+ */
+int eo_split_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                 void* planes, int64_t ldo, int64_t strideo, int64_t plane_stride, void* stream);
 
 /*
  * Bytes of scratch eo_sumsq_f32 needs for `batch` matrices of rows x cols.

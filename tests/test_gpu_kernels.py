@@ -1,0 +1,158 @@
+"""Parity of the CUDA kernels, called through the C ABI (ctypes), against the numpy oracle and, for integer-valued
+inputs where bf16 products and fp32 sums are exact, bit for bit against fp32 matmul."""
+
+import numpy as np
+import pytest
+import torch
+
+from emerging_optimizers_b200 import _native as nat
+from emerging_optimizers_b200 import triton_kernels as tk
+from oracle import ns_oracle as orc
+from tests._torch_ref import int_tensor, randn_tensor, rel_fro
+
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert nat.read_device_status() == 0
+
+
+def _exact_ref(a, c, alpha, beta):
+    ref = alpha * (a.float() @ a.float().mT)
+    if c is not None:
+        ref = ref + beta * c.float()
+    return ref.bfloat16()
+
+
+@pytest.mark.parametrize(
+    "n,k",
+    [(8, 8), (128, 64), (136, 72), (256, 256), (384, 1024), (512, 256), (1000, 136), (2048, 1024), (2304, 192)],
+)
+@pytest.mark.parametrize("trans", [False, True])
+def test_syrk_integer_inputs_bit_exact(n, k, trans):
+    a = int_tensor(n, k, seed=n + k) if not trans else int_tensor(k, n, seed=n + k).T
+    got = tk.tsyrk_ex(a)
+    assert got.is_contiguous() and got.dtype == torch.bfloat16
+    assert torch.equal(got, _exact_ref(a, None, 1.0, 0.0))
+    assert torch.equal(got, got.T)
+
+
+@pytest.mark.parametrize("n,k", [(128, 64), (520, 264), (1024, 512)])
+@pytest.mark.parametrize("trans", [False, True])
+def test_syrk_with_c_alpha_beta_bit_exact(n, k, trans):
+    a = int_tensor(n, k, seed=1) if not trans else int_tensor(k, n, seed=1).T
+    c = int_tensor(n, n, seed=2)
+    c = (c + c.T).contiguous()
+    for cc in (c, c.T):
+        got = tk.tsyrk_ex(a, cc, alpha=2**-1, beta=2**-2)
+        assert torch.equal(got, _exact_ref(a, c, 0.5, 0.25))
+    out = torch.full((n, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ret = tk.tsyrk_ex_small_matrix(a, c, alpha=0.5, beta=0.25, out=out)
+    assert ret is out and torch.equal(out, _exact_ref(a, c, 0.5, 0.25))
+
+
+def test_syrk_skip_upper_leaves_upper_untouched():
+    n, k = 520, 136
+    a = int_tensor(n, k, seed=3)
+    out = torch.full((n, n), -7.0, dtype=torch.bfloat16, device="cuda")
+    tk.tsyrk_ex_small_matrix(a, skip_upper_triangle=True, out=out)
+    ref = _exact_ref(a, None, 1.0, 0.0)
+    assert torch.equal(torch.tril(out), torch.tril(ref))
+    upper = torch.triu(torch.ones(n, n, dtype=torch.bool, device="cuda"), diagonal=1)
+    assert bool((out[upper] == -7.0).all())
+
+
+@pytest.mark.parametrize("batch,n,k", [(1, 128, 64), (3, 512, 256), (5, 136, 72), (7, 1032, 264)])
+@pytest.mark.parametrize("trans", [False, True])
+def test_batched_syrk_bit_exact(batch, n, k, trans):
+    a = int_tensor(batch, n, k, seed=4) if not trans else int_tensor(batch, k, n, seed=4).mT
+    c = int_tensor(batch, n, n, seed=5)
+    c = (c + c.mT).contiguous()
+    assert tk.can_use_batched_tsyrk(a, c)
+    got = tk.batched_tsyrk_ex(a)
+    assert torch.equal(got, _exact_ref(a, None, 1.0, 0.0))
+    got = tk.batched_tsyrk_ex(a, c, alpha=0.25, beta=0.5)
+    assert torch.equal(got, _exact_ref(a, c, 0.25, 0.5))
+    assert torch.equal(got, got.mT)
+
+
+def test_syrk_random_inputs_match_oracle():
+    a = (randn_tensor(384, 1024, seed=6) / 32).bfloat16()
+    c = randn_tensor(384, 384, seed=7)
+    c = (c + c.T).bfloat16()
+    got = tk.tsyrk_ex(a, c, alpha=1.5, beta=-0.75).float().cpu().numpy()
+    want = orc.syrk_ex(a.float().cpu().numpy(), c.float().cpu().numpy(), alpha=1.5, beta=-0.75)
+    # fp32 accumulation order differs from the oracle's BLAS: allow one bf16 ulp on isolated elements.
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 2e-3
+    assert np.array_equal(got, got.T)
+
+
+@pytest.mark.parametrize("a_mn", [0, 1])
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("m,n,k,batch", [(128, 256, 64, 1), (200, 304, 72, 1), (256, 512, 1024, 3), (1024, 2048, 520, 1)])
+def test_gemm_all_operand_layouts_bit_exact(a_mn, b_mn, m, n, k, batch):
+    lead = (batch,) if batch > 1 else ()
+    a = int_tensor(*lead, m, k, seed=8) if not a_mn else int_tensor(*lead, k, m, seed=8).mT
+    b = int_tensor(*lead, k, n, seed=9) if b_mn else int_tensor(*lead, n, k, seed=9).mT
+    c = int_tensor(*lead, m, n, seed=10)
+    out = torch.empty(*lead, m, n, dtype=torch.bfloat16, device="cuda")
+    nat.gemm(a, b, c, out, alpha=0.5, beta=0.25)
+    ref = (0.5 * (a.float() @ b.float()) + 0.25 * c.float()).bfloat16()
+    assert torch.equal(out, ref)
+    out32 = torch.empty(*lead, m, n, dtype=torch.float32, device="cuda")
+    nat.gemm(a, b, c, out32, alpha=0.5, beta=0.25, post_scale=3.0, round_bf16=True)
+    assert torch.equal(out32, ref.float() * 3.0)
+
+
+def test_config2_batched_syrk_full_size_properties():
+    """BASELINE config 2 shape: 32 x (2048 x 8192), entries N(0, 1/8192) so that diag(A) is about 1."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = (torch.randn(32, 2048, 8192, generator=g, device="cuda") / 8192**0.5).bfloat16()
+    a = tk.batched_tsyrk_ex(x)
+    assert torch.equal(a, a.mT)
+    # fp32-accumulated reference on a batch subset, tolerance 1e-2 relative as the config states
+    for b in (0, 17, 31):
+        ref = x[b].float() @ x[b].float().T
+        assert rel_fro(a[b].float(), ref) <= 1e-2
+        assert torch.allclose(a[b].float(), ref, rtol=1e-2, atol=1e-2)
+    # size-independent check on every matrix: trace(A_b) = ||X_b||_F^2
+    tr = a.float().diagonal(dim1=-2, dim2=-1).sum(-1)
+    ss = (x.float() ** 2).sum(dim=(-2, -1))
+    assert torch.allclose(tr, ss, rtol=2e-3)
+
+
+@pytest.mark.parametrize("shape", [(1024, 4096), (3, 100, 36), (7, 13), (2, 64, 64)])
+def test_sumsq_and_normalize_match_numpy(shape):
+    x = randn_tensor(*shape, seed=11, scale=1e-3)
+    ss = nat.sumsq(x).cpu().numpy()
+    xn = x.cpu().numpy()
+    want = (xn.astype(np.float64) ** 2).reshape(-1 if len(shape) == 2 else shape[0], *shape[-2:]).sum(axis=(-2, -1))
+    assert np.allclose(ss, want.reshape(ss.shape), rtol=1e-12)
+    y32 = nat.normalize(x, nat.sumsq(x), 1e-15, True, torch.float32).cpu().numpy()
+    assert np.allclose(y32, orc.frobenius_normalize(xn), rtol=2e-7, atol=0)
+    y16 = nat.normalize(x, nat.sumsq(x), 1e-15, True, torch.bfloat16).float().cpu().numpy()
+    assert np.array_equal(y16, orc.bf16_round(y32))
+    # a transposed view normalises to the transposed result
+    yt = nat.normalize(x.mT, nat.sumsq(x.mT), 1e-15, True, torch.float32)
+    assert torch.equal(yt.mT.contiguous().cpu(), torch.from_numpy(y32))
+
+
+def test_normalize_eps_clamp_and_double_mode():
+    x = torch.zeros(4, 8, device="cuda")
+    y = nat.normalize(x, nat.sumsq(x), 1e-15, True, torch.float32)
+    assert torch.equal(y, x)
+    tiny = randn_tensor(8, 16, seed=12, scale=1e-25)
+    ss = nat.sumsq(tiny)
+    assert float(ss) > 0.0  # float64 accumulation: squares of 1e-25 do not underflow
+    y = nat.normalize(tiny, ss, 1e-15, False, torch.float32).cpu().numpy()
+    assert np.allclose(y, orc.frobenius_normalize(tiny.cpu().numpy(), in_double=True), rtol=1e-6)
+
+
+def test_run_to_run_determinism():
+    a = (randn_tensor(1024, 2048, seed=13) / 45).bfloat16()
+    first = tk.tsyrk_ex(a)
+    for _ in range(10):
+        assert torch.equal(tk.tsyrk_ex(a), first)
