@@ -64,6 +64,33 @@ _PROTOTYPES: dict[str, tuple] = {
 }
 
 
+# Kernel launches issued through this module since import (what a benchmark reports as its own launches), and an
+# optional per-launch timing hook: when `launch_timer` is a list, every tensor-core launch appends
+# (name, start_event, end_event) recorded on the launching stream.
+launch_count = 0
+launch_timer: list | None = None
+
+
+class _Timed:
+    """Count the kernels one C call launches and, if asked, bracket it with CUDA events on its stream."""
+
+    def __init__(self, name: str, kernels: int, device: torch.device, timed: bool = False):
+        self.name, self.kernels, self.device, self.timed = name, kernels, device, timed
+
+    def __enter__(self) -> None:
+        global launch_count
+        launch_count += self.kernels
+        if self.timed and launch_timer is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+
+    def __exit__(self, *exc) -> None:
+        if self.timed and launch_timer is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.device))
+            launch_timer.append((self.name, self.start, end))
+
+
 class NativeLibraryError(RuntimeError):
     """Raised when ``libeo_b200.so`` is missing or one of its entry points reports a failure."""
 
@@ -166,7 +193,7 @@ class Split3:
         self.planes = torch.empty((3, batch, mat), dtype=torch.bfloat16, device=x.device)
         self.mn, self.ld, self.bstride, self.plane_stride = mn, ldo, mat, batch * mat
         self.shape, self.batch, self.device = tuple(x.shape), batch, x.device
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _Timed("split", 1, x.device):
             rc = lib().eo_split_f32(
                 x.data_ptr(), batch, rows, cols, ld, bs, self.planes.data_ptr(), ldo, mat, self.plane_stride, _stream(x)
             )
@@ -234,7 +261,7 @@ def gemm(
         ldc, sc = 0, 0
     d_mn, ldd, sd = _mat_layout(out)
     assert d_mn == 0, "out must be row-major"
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Timed("gemm", 1, out.device, timed=True):
         rc = lib().eo_gemm(
             pa, a_mn, lda, sa, pla,
             pb, bt_mn, ldb, sb, plb,
@@ -271,7 +298,7 @@ def syrk(
     d_mn, ldd, sd = _mat_layout(out)
     assert d_mn == 0, "out must be row-major"
     assert out.dtype == (torch.float32 if split else torch.bfloat16)
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Timed("syrk", 1, out.device, timed=True):
         rc = lib().eo_syrk(
             pa, a_mn, lda, sa, pla,
             c.data_ptr() if c is not None else None, ldc, sc,
@@ -291,7 +318,7 @@ def sumsq(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty(batch, dtype=torch.float64, device=x.device)
     nbytes = lib().eo_sumsq_scratch_bytes(batch, rows, cols)
     scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _Timed("sumsq", 2, x.device):
         rc = lib().eo_sumsq_f32(
             x.data_ptr(), batch, rows, cols, ld, bs, out.data_ptr(), scratch.data_ptr(), nbytes, _stream(x)
         )
@@ -315,7 +342,7 @@ def normalize(
     # Output keeps the orientation of the input: dense row-major over the physical (rows, cols).
     shape = (batch, rows, cols) if x.dim() == 3 else (rows, cols)
     out = torch.empty(shape, dtype=out_dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _Timed("normalize", 1, x.device):
         rc = lib().eo_normalize_f32(
             x.data_ptr(), batch, rows, cols, ld, bs, sumsq_.data_ptr(), eps, 1 if clamp_eps else 0,
             out.data_ptr(), cols, rows * cols, 1 if out_dtype == torch.float32 else 0, 1 if round_bf16 else 0,
