@@ -56,6 +56,11 @@ _PROTOTYPES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p],
     ),
+    "eo_sumsq_f32_noalloc": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p],
+    ),
+    "eo_sumsq_noalloc_max_partials": (c_size_t, []),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -323,6 +328,25 @@ def sumsq(x: torch.Tensor) -> torch.Tensor:
             x.data_ptr(), batch, rows, cols, ld, bs, out.data_ptr(), scratch.data_ptr(), nbytes, _stream(x)
         )
     _check(rc, "eo_sumsq_f32")
+    return out
+
+
+def sumsq_noalloc(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """:func:`sumsq` into a caller-provided float64 ``out`` through ``eo_sumsq_f32_noalloc``: the partial sums go
+    to a fixed array inside the library, so nothing is allocated on the way (neither here nor in the library).
+
+    Meant for callers that must not allocate device memory (allocator hooks, fixed-footprint loops, hosts that
+    only hold raw device pointers).  Raises for requests beyond the built-in capacity.  Calls that may overlap on
+    one GPU must be serialised by the caller: they share the array.
+    """
+    require_cuda(x, "x")
+    batch = x.size(0) if x.dim() == 3 else 1
+    assert out.dtype == torch.float64 and out.numel() == batch and out.is_contiguous() and out.device == x.device
+    mn, ld, bs = _mat_layout(x)
+    rows, cols = (x.size(-2), x.size(-1)) if mn == 0 else (x.size(-1), x.size(-2))
+    with torch.cuda.device(x.device), _Timed("sumsq", 2, x.device):
+        rc = lib().eo_sumsq_f32_noalloc(x.data_ptr(), batch, rows, cols, ld, bs, out.data_ptr(), _stream(x))
+    _check(rc, "eo_sumsq_f32_noalloc")
     return out
 
 

@@ -36,10 +36,17 @@ int fail(int code, const char* fmt, ...) {
 // Kernels report bounded-wait failures here; one copy per device that loads the module.
 __device__ unsigned int g_device_status = 0;
 
+// Scratch of eo_sumsq_f32_noalloc: per-block partial sums, resident on every device that loads this library
+// until the process exits (512 KiB).  Host code must not pass this name to a kernel: on the host it is only a
+// handle for cudaGetSymbolAddress, which device_setup() resolves once per device.
+constexpr size_t kNoAllocMaxPartials = 65536;
+static __device__ __align__(256) double g_noalloc_partials[kNoAllocMaxPartials];
+
 struct DeviceInfo {
   bool ready = false;
   int sm_count = 0;
   unsigned int* status_ptr = nullptr;
+  double* noalloc_partials = nullptr;  // device address of g_noalloc_partials on this device
 };
 constexpr int kMaxDevices = 64;
 DeviceInfo g_dev[kMaxDevices];
@@ -60,6 +67,7 @@ int device_setup(DeviceInfo** out) {
                   prop.minor);
     d.sm_count = prop.multiProcessorCount;
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_device_status));
+    EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.noalloc_partials), g_noalloc_partials));
     EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
     if (g_encode == nullptr) {
@@ -305,6 +313,29 @@ int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t 
   if (rows > 0 && cols > 0 && x == nullptr) return fail(EO_ERR_BAD_ARG, "x is NULL");
   eo::launch_sumsq(x, batch, rows, cols, ld, stride, sumsq, static_cast<double*>(scratch),
                    static_cast<cudaStream_t>(stream));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }
+
+int eo_sumsq_f32_noalloc(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                         double* sumsq, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (batch == 0) return EO_OK;
+  if (sumsq == nullptr) return fail(EO_ERR_BAD_ARG, "sumsq is NULL");
+  if (ld < cols) return fail(EO_ERR_BAD_ARG, "ld smaller than cols");
+  if (rows > 0 && cols > 0 && x == nullptr) return fail(EO_ERR_BAD_ARG, "x is NULL");
+  const size_t need = static_cast<size_t>(batch) * eo::sumsq_blocks_per_matrix(rows, cols);
+  if (need > kNoAllocMaxPartials)
+    return fail(EO_ERR_WORKSPACE,
+                "eo_sumsq_f32_noalloc: %d matrices of %lld x %lld need %zu partial sums, the built-in scratch holds "
+                "%zu; use eo_sumsq_f32 with caller-provided scratch",
+                batch, (long long)rows, (long long)cols, need, kNoAllocMaxPartials);
+  // Every partial this call reads back is written by it first, so stale contents of the shared array are harmless.
+  eo::launch_sumsq(x, batch, rows, cols, ld, stride, sumsq, dev->noalloc_partials, static_cast<cudaStream_t>(stream));
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }

@@ -128,6 +128,34 @@ int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t 
                  double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * Same result as eo_sumsq_f32, bit for bit, for callers that cannot hand over device scratch.
+ * (No counterpart in the reference; added for this library's embedders.)
+ *
+ * Who needs it: code that runs where device allocation is off the table - inside a framework's
+ * allocator callback or memory-pool trim hook, in a hot loop that has promised its owner a fixed
+ * memory footprint, or in a host that only receives raw device pointers from another runtime and has
+ * no allocator of its own to ask for a scratch buffer.  For them the per-block partial sums live in an
+ * array compiled into the library image (65536 doubles = 512 KiB, held by every GPU that loads the
+ * library until the process exits).  The call itself makes no cudaMalloc / cudaFree and calls no
+ * allocating routine.
+ *
+ * Limits and rules:
+ *   - batch * blocks_per_matrix must not exceed eo_sumsq_noalloc_max_partials() (a matrix uses
+ *     ceil(rows * cols / 32768) blocks, at most 1024); larger requests fail with EO_ERR_WORKSPACE and
+ *     launch nothing - use eo_sumsq_f32 for those;
+ *   - the array is shared by every call on a device and keeps whatever the last call left; nothing
+ *     needs clearing because each call overwrites every slot it later reads, but two calls whose
+ *     kernels may overlap on one GPU (different streams, different threads) race on it: serialise them;
+ *   - the first call of any entry point of this library on a device resolves the array's device
+ *     address (and does the other one-time set-up); make that first call outside stream capture.
+ */
+int eo_sumsq_f32_noalloc(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                         double* sumsq, void* stream);
+
+/* Capacity of the built-in scratch of eo_sumsq_f32_noalloc, in partial sums (doubles). */
+size_t eo_sumsq_noalloc_max_partials(void);
+
+/*
  * out[b] = x[b] / denom[b],  denom[b] = (float)sqrt(sumsq[b]), clamped from below by eps when
  * `clamp_eps` is set.  Output is bf16 (out_fp32 == 0) or fp32; with out_fp32 and round_bf16 the
  * quotient is rounded to bf16 and widened again.
