@@ -1,0 +1,244 @@
+"""Layer-parallel Muon: each rank orthogonalizes 1/P of the parameter matrices, then the ranks all-gather the
+orthogonalized updates and every rank applies all of them.
+
+The reference only describes this scheme in prose (``docs/primer/layerwise-distributed-optimizer.md:24-33, 39-87``
+there) and points at an external implementation; the single-process ``Muon.step`` over *all* matrices is its
+specification: after :meth:`LayerParallelMuon.step` every rank holds exactly the parameters that a single process
+would hold.
+
+Design for one NVSwitch box (one process per GPU, NCCL through ``torch.distributed``):
+
+- Matrices are independent units.  They are assigned to ranks by longest-processing-time-first on the cost
+  ``m (m + 1) n + m^2 (m + 1) + 2 m^2 n`` (tensor-core FLOPs of one iteration, m <= n).  Gradients are assumed to
+  be identical on all ranks already (the data-parallel reduction happens upstream of the optimizer).
+- The owner keeps the momentum buffer of a matrix (1/P of the optimizer state per rank), updates it, applies
+  Nesterov and runs Newton-Schulz.  On the bf16 path the Newton-Schulz result is bf16-valued, so it is exchanged
+  as bf16 without loss: 2 bytes per parameter cross NVLink instead of 4.
+- The exchange is one ``all_gather_into_tensor`` per bucket of matrices, issued on a side stream as soon as the
+  bucket's matrices are done, so it overlaps the Newton-Schulz work of the next bucket.
+- Weight decay and ``p -= lr * scale * update`` are then applied by every rank to every matrix with the same fp32
+  arithmetic, which makes the parameters bitwise identical across ranks and equal to the single-process result.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Iterable, Sequence
+
+import torch
+import torch.distributed as dist
+
+from emerging_optimizers_b200 import mixin, utils
+from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+from emerging_optimizers_b200.orthogonalized_optimizers.muon import get_muon_scale_factor
+
+
+__all__ = ["ns_cost", "partition_by_cost", "LayerParallelMuon"]
+
+
+def ns_cost(shape: Sequence[int]) -> float:
+    """Tensor-core FLOPs of one Newton-Schulz iteration on a matrix of this shape (symmetric outputs once)."""
+    m, n = sorted((int(shape[-2]), int(shape[-1])))
+    batch = 1
+    for s in shape[:-2]:
+        batch *= int(s)
+    return batch * (m * (m + 1.0) * n + m * m * (m + 1.0) + 2.0 * m * m * n)
+
+
+def partition_by_cost(costs: Sequence[float], world: int) -> list[int]:
+    """Owner rank of every item: largest cost first onto the least loaded rank (ties: lower index, lower rank).
+
+    Deterministic, so every rank computes the same assignment without communication.
+    """
+    if world < 1:
+        raise ValueError(f"world must be at least 1, got {world}")
+    owners = [0] * len(costs)
+    load = [0.0] * world
+    for i in sorted(range(len(costs)), key=lambda j: (-costs[j], j)):
+        r = min(range(world), key=lambda q: (load[q], q))
+        owners[i] = r
+        load[r] += costs[i]
+    return owners
+
+
+@dataclass
+class _Bucket:
+    """One exchange: for every rank the (parameter index, offset in the rank's slot) pairs it contributes."""
+
+    per_rank: list[list[tuple[int, int]]] = field(default_factory=list)
+    slot_numel: int = 0
+
+
+def _plan_buckets(numels: Sequence[int], owners: Sequence[int], world: int, bucket_numel: int) -> list[_Bucket]:
+    """Cut every rank's owned list into consecutive groups; group j of all ranks forms bucket j.
+
+    A group is closed once it holds ``bucket_numel`` elements.  The slot size of a bucket is the largest group in
+    it (rounded up to 8 elements), so the all-gather has equal-sized slots.
+    """
+    owned: list[list[int]] = [[] for _ in range(world)]
+    for i, r in enumerate(owners):
+        owned[r].append(i)
+    groups: list[list[list[tuple[int, int]]]] = []
+    for r in range(world):
+        mine: list[list[tuple[int, int]]] = [[]]
+        fill = 0
+        for i in owned[r]:
+            if fill >= bucket_numel and mine[-1]:
+                mine.append([])
+                fill = 0
+            mine[-1].append((i, fill))
+            fill += (numels[i] + 7) // 8 * 8
+        groups.append(mine if mine[-1] or len(mine) > 1 else [[]])
+    n_buckets = max(len(g) for g in groups)
+    buckets = []
+    for j in range(n_buckets):
+        b = _Bucket(per_rank=[g[j] if j < len(g) else [] for g in groups])
+        for r in range(world):
+            for i, off in b.per_rank[r]:
+                b.slot_numel = max(b.slot_numel, off + (numels[i] + 7) // 8 * 8)
+        buckets.append(b)
+    return buckets
+
+
+class LayerParallelMuon(mixin.WeightDecayMixin):
+    """Muon over 2-D parameters with the Newton-Schulz work divided among the ranks of ``group``.
+
+    Hyper-parameters have the meaning they have for :class:`~emerging_optimizers_b200.orthogonalized_optimizers.Muon`.
+    ``step()`` must be called by all ranks of the group, with identical gradients on all of them.
+
+    Args:
+        params: the 2-D parameters, in the same order on every rank.
+        group: process group to divide the work over (``None``: the default group; a single process if
+            torch.distributed is not initialised).
+        bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier.
+        exchange_dtype: dtype of the gathered updates.  ``None`` picks bf16 on the "medium" path (lossless there)
+            and fp32 otherwise.
+    """
+
+    def __init__(
+        self,
+        params: Iterable[torch.nn.Parameter],
+        lr: float = 3e-4,
+        momentum: float = 0.95,
+        weight_decay: float = 0.01,
+        *,
+        nesterov: bool = False,
+        weight_decay_method: mixin.WeightDecayT = "decoupled",
+        fp32_matmul_prec: utils.FP32MatmulPrecT = "medium",
+        coefficient_type: muon_utils.NSCoeffT = "quintic",
+        num_ns_steps: int = 5,
+        scale_mode: str = "spectral",
+        extra_scale_factor: float = 1.0,
+        use_syrk: bool = False,
+        group: "dist.ProcessGroup | None" = None,
+        bucket_numel: int = 64 * 1024 * 1024,
+        exchange_dtype: torch.dtype | None = None,
+    ) -> None:
+        if num_ns_steps < 1:
+            raise ValueError(f"num_ns_steps must be at least 1, got {num_ns_steps}")
+        self.params = list(params)
+        for p in self.params:
+            if p.ndim != 2:
+                raise ValueError("Only 2D parameters are supported.")
+        self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
+        self.nesterov, self.weight_decay_method = nesterov, weight_decay_method
+        self.fp32_matmul_prec = fp32_matmul_prec
+        self.coefficient_type, self.num_ns_steps = coefficient_type, num_ns_steps
+        self.scale_mode, self.extra_scale_factor, self.use_syrk = scale_mode, extra_scale_factor, use_syrk
+        self.group = group
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        self.exchange_dtype = exchange_dtype or (torch.bfloat16 if fp32_matmul_prec == "medium" else torch.float32)
+
+        self.owners = partition_by_cost([ns_cost(p.shape) for p in self.params], self.world)
+        self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel)
+        self.state: dict[int, dict[str, torch.Tensor]] = {}
+        self._side: "torch.cuda.Stream | None" = None
+
+    # -- pieces of the step ------------------------------------------------------------------------------
+    def owned_indices(self) -> list[int]:
+        return [i for i, r in enumerate(self.owners) if r == self.rank]
+
+    def _orthogonalize_owned(self, i: int) -> torch.Tensor:
+        """Momentum update, Nesterov and Newton-Schulz for parameter ``i`` (owned by this rank); unscaled."""
+        p = self.params[i]
+        if p.grad is None:
+            raise RuntimeError(f"parameter {i} has no gradient; layer-parallel Muon needs all gradients")
+        grad = p.grad
+        if self.weight_decay_method == "l2" and self.weight_decay != 0.0:
+            grad = grad.add(p, alpha=self.weight_decay)
+        st = self.state.setdefault(i, {})
+        if "momentum_buffer" not in st:
+            st["momentum_buffer"] = torch.zeros_like(p.data)
+        buf = st["momentum_buffer"]
+        buf.lerp_(grad, 1 - self.momentum)
+        update = grad.lerp(buf, self.momentum) if self.nesterov else buf
+        with utils.fp32_matmul_precision(self.fp32_matmul_prec):
+            return muon_utils.newton_schulz(
+                update, steps=self.num_ns_steps, coefficient_type=self.coefficient_type, use_syrk=self.use_syrk
+            )
+
+    def _apply(self, i: int, orth: torch.Tensor) -> None:
+        """Weight decay and ``p -= lr * (orth * scale * extra)`` with the arithmetic of the single-process step."""
+        p = self.params[i]
+        if self.weight_decay_method != "l2":
+            self._apply_weight_decay_inplace(p.data, p.grad, self.lr, self.weight_decay)
+        scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode)
+        p.data.add_(orth.to(torch.float32) * scale * self.extra_scale_factor, alpha=-self.lr)
+
+    @torch.no_grad()
+    def step(self) -> None:
+        """One optimizer step; on return every rank holds the same updated parameters."""
+        if self.world == 1:
+            for i in range(len(self.params)):
+                self._apply(i, self._orthogonalize_owned(i))
+            return
+
+        dev = self.params[0].device
+        on_gpu = dev.type == "cuda"
+        if on_gpu and self._side is None:
+            self._side = torch.cuda.Stream(device=dev)
+        pending = []
+        for b in self.buckets:
+            slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
+            for i, off in b.per_rank[self.rank]:
+                orth = self._orthogonalize_owned(i)
+                slot[off : off + orth.numel()].copy_(orth.reshape(-1))
+            gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
+            if on_gpu:
+                ready = torch.cuda.Event()
+                ready.record()
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(ready)
+                    dist.all_gather_into_tensor(gathered, slot, group=self.group)
+                    done = torch.cuda.Event()
+                    done.record()
+                slot.record_stream(self._side)
+                gathered.record_stream(self._side)
+            else:
+                dist.all_gather_into_tensor(gathered, slot, group=self.group)
+                done = None
+            pending.append((b, gathered, done))
+        for b, gathered, done in pending:
+            if done is not None:
+                torch.cuda.current_stream().wait_event(done)
+            for r in range(self.world):
+                base = r * b.slot_numel
+                for i, off in b.per_rank[r]:
+                    p = self.params[i]
+                    self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p))
+
+    # -- checkpointing -----------------------------------------------------------------------------------
+    def state_dict(self) -> dict:
+        """This rank's momentum buffers keyed by parameter index, plus the ownership map.  A full checkpoint is
+        the union over ranks."""
+        return {
+            "owners": list(self.owners),
+            "momentum_buffer": {i: st["momentum_buffer"] for i, st in self.state.items()},
+        }
+
+    def load_state_dict(self, sd: dict) -> None:
+        for i, buf in sd["momentum_buffer"].items():
+            if self.owners[int(i)] == self.rank:
+                self.state.setdefault(int(i), {})["momentum_buffer"] = buf.to(self.params[int(i)].device)
