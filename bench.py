@@ -397,6 +397,90 @@ def run_gpu_arm(args) -> None:
         dist.destroy_process_group()
 
 
+def run_muon_step(args) -> None:
+    """Secondary workload (BASELINE config 3): one Muon step over a Llama-3-8B-shaped parameter set, 32 layers of
+    q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336; fp32 params, bf16-rounded N(0, 1e-3)
+    gradients, Nesterov momentum 0.95, lr 0.02, decoupled weight decay 0.1, shape_scaling, five "simple" steps.
+    On N > 1 GPUs the matrices are divided among the ranks (layer-parallel) and the bf16 updates all-gathered;
+    total work is fixed, so scaling is "strong"."""
+    import torch
+    import torch.distributed as dist
+
+    from emerging_optimizers_b200 import _native
+    from emerging_optimizers_b200.distributed import LayerParallelMuon
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    layers = args.layers
+    layer = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336)]
+    g = torch.Generator(device=dev).manual_seed(2)
+    params = []
+    for _ in range(layers):
+        for s in layer:
+            p = torch.nn.Parameter(torch.randn(*s, generator=g, device=dev) * 0.02)
+            p.grad = (torch.randn(*s, generator=g, device=dev) * 1e-3).bfloat16().float()
+            params.append(p)
+    opt = LayerParallelMuon(params, lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True,
+                            weight_decay_method="decoupled", num_ns_steps=5, scale_mode="shape_scaling",
+                            coefficient_type="simple", fp32_matmul_prec="medium", use_syrk=True)  # fmt: skip
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 1)):
+        opt.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _native.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        opt.step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else {}
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    # checksum over ranks: parameters must be identical everywhere
+    chk = torch.stack([p.detach().double().sum() for p in params[:: max(1, len(params) // 16)]]).sum().reshape(1)
+    same = True
+    if world > 1:
+        lo, hi = chk.clone(), chk.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool((lo == hi).all())
+    status = _native.read_device_status(dev)
+    if rank == 0:
+        dense = layers * sum(flops(min(s), max(s), NS_STEPS)[0] for s in layer)
+        sym = layers * sum(flops(min(s), max(s), NS_STEPS)[1] for s in layer)
+        print(json.dumps({
+            "metric": "muon_step_ms", "value": float(t[0]), "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 1), "ms_per_step": float(t[0]), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"Muon step, Llama-3-8B-shaped parameter set ({layers} layers, {len(params)} matrices, "
+                       f"{sum(p.numel() for p in params) / 1e9:.2f} G parameters), layer-parallel x{world}",
+                       "l2": "parameter set far larger than L2"},
+            "tflops_dense_eq": dense / (float(t[0]) / 1e3) / 1e12, "tflops_sym": sym / (float(t[0]) / 1e3) / 1e12,
+            "params_identical_across_ranks": same, "gpu_launches": (_native.launch_count - launches0),
+            "clocks": clocks, "device_status": status,
+        }), flush=True)  # fmt: skip
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -408,12 +492,17 @@ def main() -> None:
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident timing only: no end-to-end loop, CPU baseline or clock sampling, and "
                     "--warmup taken as given (for profiler captures; not a benchmark number)")
+    ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step"],
+                    help="newton_schulz (default, the headline metric) or muon_step (BASELINE config 3)")
+    ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
     args = ap.parse_args()
     if args.shape is not None:
         global M, N_COLS
         M, N_COLS = args.shape
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "muon_step":
+        run_muon_step(args)
     else:
         run_gpu_arm(args)
 

@@ -61,6 +61,16 @@ _PROTOTYPES: dict[str, tuple] = {
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p],
     ),
     "eo_sumsq_noalloc_max_partials": (c_size_t, []),
+    "eo_muon_scratch_bytes": (c_size_t, [c_int64]),
+    "eo_muon_momentum_f32": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_double, c_int, c_float, c_void_p, c_void_p, c_size_t, c_void_p],
+    ),
+    "eo_muon_normalize_bf16": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_double, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p],
+    ),
+    "eo_muon_apply_f32": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_float, c_float, c_float, c_float, c_void_p]),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -374,3 +384,50 @@ def normalize(
         )  # fmt: skip
     _check(rc, "eo_normalize_f32")
     return out.mT if mn == 1 else out
+
+
+def muon_momentum(
+    g: torch.Tensor, m: torch.Tensor, p: torch.Tensor | None, momentum: float, nesterov: bool, l2: float
+) -> torch.Tensor:
+    """Update the momentum buffer ``m`` in place and return the float64 sum of squares (shape (1,)) of the tensor
+    that will be orthogonalized; see ``eo_muon_momentum_f32``.  All tensors flat-contiguous fp32."""
+    require_cuda(g, "g")
+    numel = g.numel()
+    out = torch.empty(1, dtype=torch.float64, device=g.device)
+    nbytes = lib().eo_muon_scratch_bytes(numel)
+    scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=g.device)
+    with torch.cuda.device(g.device), _Timed("muon_momentum", 2, g.device):
+        rc = lib().eo_muon_momentum_f32(
+            g.data_ptr(), m.data_ptr(), p.data_ptr() if (p is not None and l2 != 0.0) else None, numel,
+            momentum, 1 if nesterov else 0, l2, out.data_ptr(), scratch.data_ptr(), nbytes, _stream(g),
+        )  # fmt: skip
+    _check(rc, "eo_muon_momentum_f32")
+    return out
+
+
+def muon_normalize(
+    g: torch.Tensor, m: torch.Tensor, p: torch.Tensor | None, momentum: float, nesterov: bool, l2: float,
+    sumsq_: torch.Tensor, eps: float, out: torch.Tensor,
+) -> torch.Tensor:  # fmt: skip
+    """Write the normalised, bf16-rounded tensor to orthogonalize into ``out`` (contiguous bf16, same numel)."""
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == g.numel()
+    with torch.cuda.device(g.device), _Timed("muon_normalize", 1, g.device):
+        rc = lib().eo_muon_normalize_bf16(
+            g.data_ptr(), m.data_ptr(), p.data_ptr() if (p is not None and l2 != 0.0) else None, g.numel(),
+            momentum, 1 if nesterov else 0, l2, sumsq_.data_ptr(), eps, out.data_ptr(), _stream(g),
+        )  # fmt: skip
+    _check(rc, "eo_muon_normalize_bf16")
+    return out
+
+
+def muon_apply(p: torch.Tensor, update: torch.Tensor, shrink: float, scale: float, extra: float, lr: float) -> None:
+    """``p <- (p + shrink * p) - lr * ((update * scale) * extra)`` in place; ``update`` bf16 or fp32, contiguous."""
+    require_cuda(p, "p")
+    assert p.is_contiguous() and update.is_contiguous() and p.numel() == update.numel() and p.dtype == torch.float32
+    assert update.dtype in (torch.bfloat16, torch.float32)
+    with torch.cuda.device(p.device), _Timed("muon_apply", 1, p.device):
+        rc = lib().eo_muon_apply_f32(
+            p.data_ptr(), update.data_ptr(), 1 if update.dtype == torch.bfloat16 else 0, p.numel(),
+            shrink, scale, extra, lr, _stream(p),
+        )  # fmt: skip
+    _check(rc, "eo_muon_apply_f32")

@@ -164,6 +164,125 @@ inline void launch_split3(const float* x, int batch, int64_t rows, int64_t cols,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Muon step, elementwise parts, on flat contiguous fp32 arrays.
+//   u(g, m', p) : g' = g + l2 * p;  m' = lerp(m, g', 1 - mu);  u = nesterov ? lerp(g', m', mu) : m'
+// with lerp(a, b, w) = |w| < 0.5 ? a + w (b - a) : b - (b - a)(1 - w)   (the formula torch.lerp uses).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float lerp_f32(float a, float b, float w) {
+  const float d = b - a;
+  return (fabsf(w) < 0.5f) ? a + w * d : b - d * (1.0f - w);
+}
+
+struct MuonEw {
+  float momentum;  // mu
+  float one_minus_momentum;  // 1 - mu, rounded once from double (the weight torch.lerp_ receives)
+  float l2;        // weight decay added to the gradient (0 unless the l2 method is used)
+  int nesterov;
+};
+
+__device__ __forceinline__ float muon_update(float g, float m_new, const MuonEw& c) {
+  return c.nesterov ? lerp_f32(g, m_new, c.momentum) : m_new;
+}
+
+// Pass 1: momentum buffer update in place and per-block partial sums of u^2.
+__global__ void __launch_bounds__(kEwThreads)
+    muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ m, const float* __restrict__ p,
+                         long long numel, MuonEw c, double* __restrict__ partial) {
+  double acc = 0.0;
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  const long long n4 = numel >> 2;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 gv = __ldg(reinterpret_cast<const float4*>(g) + i);
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    if (c.l2 != 0.0f) {
+      const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
+      gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
+    }
+    const float w = c.one_minus_momentum;
+    mv.x = lerp_f32(mv.x, gv.x, w); mv.y = lerp_f32(mv.y, gv.y, w);
+    mv.z = lerp_f32(mv.z, gv.z, w); mv.w = lerp_f32(mv.w, gv.w, w);
+    reinterpret_cast<float4*>(m)[i] = mv;
+    const double u0 = muon_update(gv.x, mv.x, c), u1 = muon_update(gv.y, mv.y, c);
+    const double u2 = muon_update(gv.z, mv.z, c), u3 = muon_update(gv.w, mv.w, c);
+    acc += u0 * u0 + u1 * u1;
+    acc += u2 * u2 + u3 * u3;
+  }
+  for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
+    float gv = g[i];
+    if (c.l2 != 0.0f) gv += c.l2 * p[i];
+    const float mv = lerp_f32(m[i], gv, c.one_minus_momentum);
+    m[i] = mv;
+    const double u = muon_update(gv, mv, c);
+    acc += u * u;
+  }
+  const double total = block_reduce_sum(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = total;
+}
+
+// Pass 2: recompute u from g and the updated momentum buffer, divide by the norm, write bf16.
+__global__ void __launch_bounds__(kEwThreads)
+    muon_normalize_kernel(const float* __restrict__ g, const float* __restrict__ m, const float* __restrict__ p,
+                          long long numel, MuonEw c, const double* __restrict__ sumsq, float eps,
+                          __nv_bfloat16* __restrict__ out) {
+  const float norm = fmaxf(static_cast<float>(sqrt(sumsq[0])), eps);
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  const long long n4 = numel >> 2;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c.nesterov || c.l2 != 0.0f) gv = __ldg(reinterpret_cast<const float4*>(g) + i);
+    if (c.nesterov && c.l2 != 0.0f) {
+      const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
+      gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
+    }
+    const float4 mv = __ldg(reinterpret_cast<const float4*>(m) + i);
+    const float q0 = muon_update(gv.x, mv.x, c) / norm, q1 = muon_update(gv.y, mv.y, c) / norm;
+    const float q2 = muon_update(gv.z, mv.z, c) / norm, q3 = muon_update(gv.w, mv.w, c) / norm;
+    uint2 t;
+    t.x = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(q0))) |
+          (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(q1))) << 16);
+    t.y = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(q2))) |
+          (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(q3))) << 16);
+    reinterpret_cast<uint2*>(out)[i] = t;
+  }
+  for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
+    float gv = g[i];
+    if (c.l2 != 0.0f) gv += c.l2 * p[i];
+    out[i] = __float2bfloat16_rn(muon_update(gv, m[i], c) / norm);
+  }
+}
+
+// Weight update: p <- (p + shrink * p) - lr * ((u * scale) * extra), the operation order of
+// `p.add_(p, alpha=shrink)` followed by `p.add_(u * scale * extra, alpha=-lr)`.
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads)
+    muon_apply_kernel(float* __restrict__ p, const U* __restrict__ u, long long numel, float shrink, float scale,
+                      float extra, float lr) {
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  for (long long i = tid; i < numel; i += nthreads) {
+    float pv = p[i];
+    if (shrink != 0.0f) pv = pv + shrink * pv;
+    float uv;
+    if constexpr (sizeof(U) == 2) {
+      uv = __bfloat162float(u[i]);
+    } else {
+      uv = u[i];
+    }
+    const float t = (uv * scale) * extra;
+    p[i] = pv + (-lr) * t;
+  }
+}
+
+inline int ew_blocks(long long numel, int per_thread) {
+  long long nb = (numel + static_cast<long long>(kEwThreads) * per_thread - 1) / (static_cast<long long>(kEwThreads) * per_thread);
+  if (nb < 1) nb = 1;
+  if (nb > 4096) nb = 4096;
+  return static_cast<int>(nb);
+}
+
 inline void launch_sumsq(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
                          double* sumsq, double* scratch, cudaStream_t stream) {
   const int nblk = sumsq_blocks_per_matrix(rows, cols);

@@ -317,6 +317,70 @@ int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t 
   return EO_OK;
 }
 
+size_t eo_muon_scratch_bytes(int64_t numel) {
+  if (numel <= 0) return 0;
+  return static_cast<size_t>(eo::sumsq_blocks_per_matrix(numel, 1)) * sizeof(double);
+}
+
+int eo_muon_momentum_f32(const float* g, float* m, const float* p, int64_t numel, double momentum, int nesterov,
+                         float l2_weight_decay, double* sumsq, void* scratch, size_t scratch_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (numel < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (g == nullptr || m == nullptr || sumsq == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (l2_weight_decay != 0.0f && p == nullptr) return fail(EO_ERR_BAD_ARG, "l2 weight decay needs p");
+  if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(p)) & 15)
+    return fail(EO_ERR_BAD_ARG, "g, m and p must be 16-byte aligned");
+  const size_t need = eo_muon_scratch_bytes(numel);
+  if (scratch_bytes < need || scratch == nullptr)
+    return fail(EO_ERR_WORKSPACE, "muon scratch: need %zu bytes, got %zu", need, scratch_bytes);
+  const int nblk = eo::sumsq_blocks_per_matrix(numel, 1);
+  eo::MuonEw c{static_cast<float>(momentum), static_cast<float>(1.0 - momentum), l2_weight_decay, nesterov ? 1 : 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  eo::muon_momentum_kernel<<<nblk, eo::kEwThreads, 0, s>>>(g, m, p, numel, c, static_cast<double*>(scratch));
+  eo::sumsq_final_kernel<<<1, eo::kEwThreads, 0, s>>>(static_cast<const double*>(scratch), nblk, sumsq);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_muon_normalize_bf16(const float* g, const float* m, const float* p, int64_t numel, double momentum,
+                           int nesterov, float l2_weight_decay, const double* sumsq, float eps, void* out,
+                           void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (numel < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (numel == 0) return EO_OK;
+  if (g == nullptr || m == nullptr || sumsq == nullptr || out == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (l2_weight_decay != 0.0f && p == nullptr) return fail(EO_ERR_BAD_ARG, "l2 weight decay needs p");
+  if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(p) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return fail(EO_ERR_BAD_ARG, "g, m, p and out must be 16-byte aligned");
+  eo::MuonEw c{static_cast<float>(momentum), static_cast<float>(1.0 - momentum), l2_weight_decay, nesterov ? 1 : 0};
+  eo::muon_normalize_kernel<<<eo::ew_blocks(numel, 16), eo::kEwThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      g, m, p, numel, c, sumsq, eps, static_cast<__nv_bfloat16*>(out));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t numel, float shrink, float scale,
+                      float extra_scale, float lr, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (numel < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (numel == 0) return EO_OK;
+  if (p == nullptr || update == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int nb = eo::ew_blocks(numel, 8);
+  if (update_is_bf16)
+    eo::muon_apply_kernel<__nv_bfloat16><<<nb, eo::kEwThreads, 0, s>>>(
+        p, static_cast<const __nv_bfloat16*>(update), numel, shrink, scale, extra_scale, lr);
+  else
+    eo::muon_apply_kernel<float><<<nb, eo::kEwThreads, 0, s>>>(p, static_cast<const float*>(update), numel, shrink,
+                                                               scale, extra_scale, lr);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
 size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }
 
 int eo_sumsq_f32_noalloc(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,

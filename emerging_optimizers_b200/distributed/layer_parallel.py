@@ -28,9 +28,9 @@ from typing import Iterable, Sequence
 import torch
 import torch.distributed as dist
 
-from emerging_optimizers_b200 import mixin, utils
-from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
-from emerging_optimizers_b200.orthogonalized_optimizers.muon import get_muon_scale_factor
+from emerging_optimizers_b200 import _native, mixin, utils
+from emerging_optimizers_b200.orthogonalized_optimizers import _fused_step, muon_utils
+from emerging_optimizers_b200.orthogonalized_optimizers.muon import _NS_FUNCTIONS, _SHRINK, get_muon_scale_factor
 
 
 __all__ = ["ns_cost", "partition_by_cost", "LayerParallelMuon"]
@@ -179,20 +179,63 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
                 update, steps=self.num_ns_steps, coefficient_type=self.coefficient_type, use_syrk=self.use_syrk
             )
 
-    def _apply(self, i: int, orth: torch.Tensor) -> None:
+    def _use_fused_kernels(self) -> bool:
+        """Static decision, identical on every rank: all parameters are contiguous fp32 CUDA matrices, the bf16
+        path is selected and the driver functions are the package's own."""
+        return (
+            self.fp32_matmul_prec == "medium"
+            and self.weight_decay_method in _SHRINK
+            and self.coefficient_type in muon_utils._COEFFICIENT_SETS
+            and all(_fused_step.eligible(p.data, p.grad) for p in self.params)
+            and all(getattr(muon_utils, name) is fn for name, fn in _NS_FUNCTIONS.items())
+        )
+
+    def _orthogonalize_many(self, idxs: Sequence[int], fused: bool) -> dict[int, torch.Tensor]:
+        """Unscaled orthogonalized updates of the owned parameters ``idxs``."""
+        if not fused:
+            return {i: self._orthogonalize_owned(i) for i in idxs}
+        for i in idxs:
+            st = self.state.setdefault(i, {})
+            if "momentum_buffer" not in st:
+                st["momentum_buffer"] = torch.zeros_like(self.params[i].data)
+        l2 = self.weight_decay if self.weight_decay_method == "l2" else 0.0
+        ups = _fused_step.orthogonalized_updates(
+            [self.params[i].data for i in idxs],
+            [self.params[i].grad for i in idxs],
+            [self.state[i]["momentum_buffer"] for i in idxs],
+            momentum=self.momentum,
+            nesterov=self.nesterov,
+            l2_weight_decay=l2,
+            steps=self.num_ns_steps,
+            coefficient_type=self.coefficient_type,
+            use_syrk=self.use_syrk,
+        )
+        return dict(zip(idxs, ups))
+
+    def _apply(self, i: int, orth: torch.Tensor, fused: bool = False) -> None:
         """Weight decay and ``p -= lr * (orth * scale * extra)`` with the arithmetic of the single-process step."""
         p = self.params[i]
+        scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode)
+        if fused:
+            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
+            _native.muon_apply(p.data, orth, shrink, scale, self.extra_scale_factor, self.lr)
+            return
         if self.weight_decay_method != "l2":
             self._apply_weight_decay_inplace(p.data, p.grad, self.lr, self.weight_decay)
-        scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode)
         p.data.add_(orth.to(torch.float32) * scale * self.extra_scale_factor, alpha=-self.lr)
 
     @torch.no_grad()
     def step(self) -> None:
         """One optimizer step; on return every rank holds the same updated parameters."""
+        for i, p in enumerate(self.params):
+            if p.grad is None:
+                raise RuntimeError(f"parameter {i} has no gradient; layer-parallel Muon needs all gradients")
+        fused = self._use_fused_kernels()
         if self.world == 1:
-            for i in range(len(self.params)):
-                self._apply(i, self._orthogonalize_owned(i))
+            for b in self.buckets:
+                idxs = [i for i, _ in b.per_rank[0]]
+                for i, orth in self._orthogonalize_many(idxs, fused).items():
+                    self._apply(i, orth, fused)
             return
 
         dev = self.params[0].device
@@ -202,9 +245,10 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         pending = []
         for b in self.buckets:
             slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
-            for i, off in b.per_rank[self.rank]:
-                orth = self._orthogonalize_owned(i)
-                slot[off : off + orth.numel()].copy_(orth.reshape(-1))
+            mine = b.per_rank[self.rank]
+            orths = self._orthogonalize_many([i for i, _ in mine], fused)
+            for i, off in mine:
+                slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
             gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
             if on_gpu:
                 ready = torch.cuda.Event()
@@ -227,7 +271,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
                 base = r * b.slot_numel
                 for i, off in b.per_rank[r]:
                     p = self.params[i]
-                    self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p))
+                    self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p), fused)
 
     # -- checkpointing -----------------------------------------------------------------------------------
     def state_dict(self) -> dict:

@@ -14,14 +14,15 @@ from torch.optim.optimizer import ParamsT
 
 from emerging_optimizers_b200 import registry, triton_kernels
 from emerging_optimizers_b200.mixin import WeightDecayT
-from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+from emerging_optimizers_b200 import _native
+from emerging_optimizers_b200.orthogonalized_optimizers import _fused_step, muon_utils
 from emerging_optimizers_b200.orthogonalized_optimizers.muon_utils import NSCoeffT
 from emerging_optimizers_b200.orthogonalized_optimizers.orthogonalized_optimizer import (
     OrthogonalizedOptimizer,
     _args_doc,
 )
 from emerging_optimizers_b200.utils import FP32MatmulPrecT
-from emerging_optimizers_b200.weight_update_hooks import WeightUpdateHook
+from emerging_optimizers_b200.weight_update_hooks import NoOpWeightUpdateHook, WeightUpdateHook
 from emerging_optimizers_b200.weight_update_hooks.base import HookStateT
 
 
@@ -31,6 +32,29 @@ MuonScaleT = Literal["shape_scaling", "spectral", "unit_rms_norm"]
 
 # Compute capabilities on which the SYRK kernel of this package runs.
 _SYRK_SM = ((10, 0), (10, 3))
+
+# Set to False to force the per-parameter step even where the grouped fused step applies.
+FUSED_STEP = True
+
+# The driver functions as defined by this package: the fused step only takes over while nobody has replaced them.
+_NS_FUNCTIONS = {
+    name: getattr(muon_utils, name)
+    for name in (
+        "newton_schulz",
+        "newton_schulz_step",
+        "batched_newton_schulz_step",
+        "newton_schulz_step_tsyrk",
+        "batched_newton_schulz_step_tsyrk",
+    )
+}
+
+# parameter shrink p <- p + f * p applied before the update, per weight-decay method ("l2" acts on the gradient)
+_SHRINK = {
+    "decoupled": lambda lr, wd: -wd * lr,
+    "independent": lambda lr, wd: -wd,
+    "palm": lambda lr, wd: -(wd * lr * lr),
+    "l2": lambda lr, wd: 0.0,
+}
 
 
 def _read_only(name: str) -> property:
@@ -116,6 +140,70 @@ class Muon(OrthogonalizedOptimizer[HookStateT]):
             scaled_orthogonalize_fn=scaled_orthogonalize_fn,
             weight_update_hook=weight_update_hook,
         )
+        self._muon_closure = scaled_orthogonalize_fn
+
+    def _fused_step_applies(self) -> bool:
+        """The grouped fused step computes exactly what the per-parameter step computes, but bypasses the
+        override points; it is used only while none of them is customised and the bf16 path is selected."""
+        cls, base = type(self), OrthogonalizedOptimizer
+        return (
+            FUSED_STEP
+            and self.fp32_matmul_prec == "medium"
+            and self.weight_decay_method in _SHRINK
+            and self._coefficient_type in muon_utils._COEFFICIENT_SETS
+            and cls.orthogonalize is base.orthogonalize
+            and cls._step_param is base._step_param
+            and cls.pre_weight_update_fn_inplace is base.pre_weight_update_fn_inplace
+            and cls.post_weight_update_fn_inplace is base.post_weight_update_fn_inplace
+            and type(self._weight_update_hook) is NoOpWeightUpdateHook
+            and self.scaled_orthogonalize_fn is self._muon_closure
+            and all(getattr(muon_utils, name) is fn for name, fn in _NS_FUNCTIONS.items())
+        )
+
+    @torch.no_grad()
+    def step(self, closure=None):  # type: ignore[no-untyped-def]
+        """One optimization step.
+
+        Parameters that the fused kernels can take (2-D contiguous fp32 CUDA tensors, bf16 path, no customised
+        hook or override) are processed as groups of equally shaped matrices: fused momentum / normalise kernels,
+        one batched Newton-Schulz run per group, fused weight update.  Everything else takes the per-parameter
+        path of the base class.  Both paths compute the same update.
+        """
+        if closure is not None:
+            raise ValueError("closure is not supported")
+        if not self._fused_step_applies():
+            return super().step()
+
+        for group in self.param_groups:
+            self._init_group(group)
+            lr, wd, mu = group["lr"], group["weight_decay"], group["momentum"]
+            fused = []
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if _fused_step.eligible(p, p.grad) and self.state[p]["momentum_buffer"].is_contiguous():
+                    fused.append(p)
+                else:
+                    self._step_param(group, p)
+            if not fused:
+                continue
+            l2 = wd if self.weight_decay_method == "l2" else 0.0
+            updates = _fused_step.orthogonalized_updates(
+                [p.data for p in fused],
+                [p.grad for p in fused],
+                [self.state[p]["momentum_buffer"] for p in fused],
+                momentum=mu,
+                nesterov=self.nesterov,
+                l2_weight_decay=l2,
+                steps=self._num_ns_steps,
+                coefficient_type=self._coefficient_type,
+                use_syrk=self._use_syrk,
+            )
+            shrink = _SHRINK[self.weight_decay_method](lr, wd) if wd != 0.0 else 0.0
+            for p, u in zip(fused, updates):
+                scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self._scale_mode)
+                _native.muon_apply(p.data, u, shrink, scale, self._extra_scale_factor, lr)
+        return None
 
     num_ns_steps = _read_only("num_ns_steps")
     coefficient_type = _read_only("coefficient_type")

@@ -108,26 +108,28 @@ class OrthogonalizedOptimizer(opt_mixin.WeightDecayMixin, optim.Optimizer, Gener
 
         for group in self.param_groups:
             self._init_group(group)
-            lr = group["lr"]
-            group_kwargs = {k: v for k, v in group.items() if k != "params"}
-
             for p in group["params"]:
-                if p.grad is None:
-                    continue
-                grad = p.grad
-                self._apply_weight_decay_inplace(p, grad, lr, group["weight_decay"])
-                update = self._momentum_update(grad, self.state[p]["momentum_buffer"], group["momentum"])
-
-                with utils.fp32_matmul_precision(self.fp32_matmul_prec):
-                    orth = self.orthogonalize(p, update, **group_kwargs)
-
-                self.pre_weight_update_fn_inplace(p, orth)
-                hook_state = self._weight_update_hook.pre_weight_update_inplace(p, orth)
-                p.add_(orth, alpha=-lr)
-                self.post_weight_update_fn_inplace(p)
-                self._weight_update_hook.post_weight_update_inplace(p, hook_state)
+                if p.grad is not None:
+                    self._step_param(group, p)
 
         return None
+
+    def _step_param(self, group: dict, p: torch.Tensor) -> None:
+        """The update of one parameter: weight decay, momentum, orthogonalize, hooks, ``p -= lr * update``."""
+        lr = group["lr"]
+        grad = p.grad
+        self._apply_weight_decay_inplace(p, grad, lr, group["weight_decay"])
+        update = self._momentum_update(grad, self.state[p]["momentum_buffer"], group["momentum"])
+
+        with utils.fp32_matmul_precision(self.fp32_matmul_prec):
+            group_kwargs = {k: v for k, v in group.items() if k != "params"}
+            orth = self.orthogonalize(p, update, **group_kwargs)
+
+        self.pre_weight_update_fn_inplace(p, orth)
+        hook_state = self._weight_update_hook.pre_weight_update_inplace(p, orth)
+        p.add_(orth, alpha=-lr)
+        self.post_weight_update_fn_inplace(p)
+        self._weight_update_hook.post_weight_update_inplace(p, hook_state)
 
     def orthogonalize(self, p: torch.Tensor, grad: torch.Tensor, **kwargs: Any) -> torch.Tensor:
         """Map the momentum tensor of ``p`` to its orthogonalized update.

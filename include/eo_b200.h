@@ -167,6 +167,33 @@ int eo_normalize_f32(const float* x, int batch, int64_t rows, int64_t cols, int6
                      const double* sumsq, float eps, int clamp_eps,
                      void* out, int64_t ldo, int64_t strideo, int out_fp32, int round_bf16, void* stream);
 
+/*
+ * Elementwise parts of one Muon step on a flat, contiguous, 16-byte-aligned fp32 parameter of `numel`
+ * elements.  With g' = g + l2_weight_decay * p, lerp(a, b, w) as torch.lerp computes it:
+ *
+ *   eo_muon_momentum_f32 : m <- lerp(m, g', 1 - momentum) in place;
+ *                          sumsq[0] = sum u^2 (float64, fixed order), u = nesterov ? lerp(g', m, momentum) : m
+ *   eo_muon_normalize_bf16: out = bf16(u / max((float)sqrt(sumsq[0]), eps)), u recomputed from g, p and the
+ *                          updated m (so u itself never goes to memory)
+ *   eo_muon_apply_f32    : p <- (p + shrink * p) - lr * ((update * scale) * extra_scale)
+ *
+ * `momentum` is a double so that 1 - momentum is rounded to fp32 once, as the weight of torch.lerp_ is.
+ * `scratch` of eo_muon_momentum_f32 must hold eo_muon_scratch_bytes(numel) bytes.  `p` may be NULL when
+ * l2_weight_decay == 0.  `update` is bf16 (update_is_bf16 != 0) or fp32.
+ *
+ * Stand in for emerging_optimizers/orthogonalized_optimizers/orthogonalized_optimizer.py:185-199 (weight
+ * decay on the gradient, `lerp_`, Nesterov `lerp`), muon_utils.py:216, 262 (normalise, bf16 cast), and
+ * mixin.py:44-52 + muon.py:131-132 + orthogonalized_optimizer.py:208 (parameter shrink, scale, `p.add_`).
+ */
+size_t eo_muon_scratch_bytes(int64_t numel);
+int eo_muon_momentum_f32(const float* g, float* m, const float* p, int64_t numel, double momentum, int nesterov,
+                         float l2_weight_decay, double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
+int eo_muon_normalize_bf16(const float* g, const float* m, const float* p, int64_t numel, double momentum,
+                           int nesterov, float l2_weight_decay, const double* sumsq, float eps, void* out,
+                           void* stream);
+int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t numel, float shrink, float scale,
+                      float extra_scale, float lr, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
