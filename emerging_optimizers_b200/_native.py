@@ -71,6 +71,22 @@ _PROTOTYPES: dict[str, tuple] = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_double, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p],
     ),
     "eo_muon_apply_f32": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_float, c_float, c_float, c_float, c_void_p]),
+    "eo_muon_prepare_scratch_bytes": (c_size_t, [c_int, c_int64]),
+    "eo_muon_prepare_batch": (
+        c_int,
+        [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_double, c_int, c_float, c_float, c_void_p, c_int64]
+        + [c_void_p, c_void_p, c_size_t, c_void_p],
+    ),
+    "eo_muon_apply_batch": (
+        c_int,
+        [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p],
+    ),
+    "eo_newton_schulz_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "eo_newton_schulz_bf16": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int]
+        + [c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+    ),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -431,3 +447,77 @@ def muon_apply(p: torch.Tensor, update: torch.Tensor, shrink: float, scale: floa
             shrink, scale, extra, lr, _stream(p),
         )  # fmt: skip
     _check(rc, "eo_muon_apply_f32")
+
+
+def _ptr_array(tensors) -> "ctypes.Array":
+    arr = (c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = t.data_ptr() if t is not None else None
+    return arr
+
+
+def muon_prepare_batch(
+    grads, momenta, params, momentum: float, nesterov: bool, l2: float, eps: float, out_stack: torch.Tensor
+) -> torch.Tensor:
+    """Momentum update of ``n`` equally sized flat-contiguous fp32 tensors and their normalised bf16 images written
+    to ``out_stack[i]``; returns the float64 sums of squares (n,).  See ``eo_muon_prepare_batch``."""
+    n = len(grads)
+    dev = grads[0].device
+    numel = grads[0].numel()
+    assert out_stack.dtype == torch.bfloat16 and out_stack.is_contiguous() and out_stack.size(0) == n
+    slot_stride = out_stack[0].numel()
+    assert slot_stride >= numel and slot_stride % 8 == 0
+    ss = torch.empty(n, dtype=torch.float64, device=dev)
+    nbytes = lib().eo_muon_prepare_scratch_bytes(n, numel)
+    scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev), _Timed("muon_prepare", 3 * ((n + 47) // 48), dev):
+        rc = lib().eo_muon_prepare_batch(
+            n, _ptr_array(grads), _ptr_array(momenta), _ptr_array(params) if l2 != 0.0 else None, numel,
+            momentum, 1 if nesterov else 0, l2, eps, out_stack.data_ptr(), slot_stride,
+            ss.data_ptr(), scratch.data_ptr(), nbytes, torch.cuda.current_stream(dev).cuda_stream,
+        )  # fmt: skip
+    _check(rc, "eo_muon_prepare_batch")
+    return ss
+
+
+def muon_apply_batch(params, updates, scales, shrink: float, extra: float, lr: float) -> None:
+    """Fused weight update of a list of contiguous fp32 parameters; ``updates`` all bf16 or all fp32."""
+    n = len(params)
+    if n == 0:
+        return
+    dev = params[0].device
+    is_bf16 = updates[0].dtype == torch.bfloat16
+    numel = (c_int64 * n)(*[p.numel() for p in params])
+    sc = (c_float * n)(*scales)
+    with torch.cuda.device(dev), _Timed("muon_apply", (n + 47) // 48, dev):
+        rc = lib().eo_muon_apply_batch(
+            n, _ptr_array(params), _ptr_array(updates), 1 if is_bf16 else 0, numel, sc, shrink, extra, lr,
+            torch.cuda.current_stream(dev).cuda_stream,
+        )  # fmt: skip
+    _check(rc, "eo_muon_apply_batch")
+
+
+def newton_schulz_bf16(
+    x: torch.Tensor, schedule, use_syrk: bool, out_dtype: torch.dtype = torch.bfloat16
+) -> torch.Tensor:
+    """Run the whole iteration loop on a normalised bf16 iterate ``x`` ((B,) rows, cols, row-major, 16-byte
+    aligned rows) with one library call; ``x`` is clobbered.  Returns a new contiguous tensor of ``out_dtype``."""
+    require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and len(schedule) >= 1
+    batch = x.size(0) if x.dim() == 3 else 1
+    rows, cols = x.size(-2), x.size(-1)
+    mn, ld, bs = _mat_layout(x)
+    assert mn == 0, "x must be row-major"
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    nbytes = lib().eo_newton_schulz_workspace_bytes(batch, rows, cols)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    abc = (c_float * (3 * len(schedule)))(*[v for t in schedule for v in t])
+    kernels = sum(3 if t[2] != 0.0 else 2 for t in schedule)
+    with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
+        rc = lib().eo_newton_schulz_bf16(
+            x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
+            1 if use_syrk else 0, out.data_ptr(), 1 if out_dtype == torch.float32 else 0, cols, rows * cols,
+            ws.data_ptr(), nbytes, _stream(x),
+        )  # fmt: skip
+    _check(rc, "eo_newton_schulz_bf16")
+    return out

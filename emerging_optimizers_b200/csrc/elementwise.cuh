@@ -186,13 +186,14 @@ __device__ __forceinline__ float muon_update(float g, float m_new, const MuonEw&
 }
 
 // Pass 1: momentum buffer update in place and per-block partial sums of u^2.
-__global__ void __launch_bounds__(kEwThreads)
-    muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ m, const float* __restrict__ p,
-                         long long numel, MuonEw c, double* __restrict__ partial) {
+__device__ __forceinline__ void muon_momentum_body(const float* __restrict__ g, float* __restrict__ m,
+                                                   const float* __restrict__ p, long long numel, const MuonEw& c,
+                                                   double* __restrict__ partial_slot) {
   double acc = 0.0;
   const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
   const long long n4 = numel >> 2;
+  const float w = c.one_minus_momentum;
   for (long long i = tid; i < n4; i += nthreads) {
     float4 gv = __ldg(reinterpret_cast<const float4*>(g) + i);
     float4 mv = reinterpret_cast<float4*>(m)[i];
@@ -200,7 +201,6 @@ __global__ void __launch_bounds__(kEwThreads)
       const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
       gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
     }
-    const float w = c.one_minus_momentum;
     mv.x = lerp_f32(mv.x, gv.x, w); mv.y = lerp_f32(mv.y, gv.y, w);
     mv.z = lerp_f32(mv.z, gv.z, w); mv.w = lerp_f32(mv.w, gv.w, w);
     reinterpret_cast<float4*>(m)[i] = mv;
@@ -212,27 +212,26 @@ __global__ void __launch_bounds__(kEwThreads)
   for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
     float gv = g[i];
     if (c.l2 != 0.0f) gv += c.l2 * p[i];
-    const float mv = lerp_f32(m[i], gv, c.one_minus_momentum);
+    const float mv = lerp_f32(m[i], gv, w);
     m[i] = mv;
     const double u = muon_update(gv, mv, c);
     acc += u * u;
   }
   const double total = block_reduce_sum(acc);
-  if (threadIdx.x == 0) partial[blockIdx.x] = total;
+  if (threadIdx.x == 0) *partial_slot = total;
 }
 
 // Pass 2: recompute u from g and the updated momentum buffer, divide by the norm, write bf16.
-__global__ void __launch_bounds__(kEwThreads)
-    muon_normalize_kernel(const float* __restrict__ g, const float* __restrict__ m, const float* __restrict__ p,
-                          long long numel, MuonEw c, const double* __restrict__ sumsq, float eps,
-                          __nv_bfloat16* __restrict__ out) {
-  const float norm = fmaxf(static_cast<float>(sqrt(sumsq[0])), eps);
+__device__ __forceinline__ void muon_normalize_body(const float* __restrict__ g, const float* __restrict__ m,
+                                                    const float* __restrict__ p, long long numel, const MuonEw& c,
+                                                    double sumsq, float eps, __nv_bfloat16* __restrict__ out) {
+  const float norm = fmaxf(static_cast<float>(sqrt(sumsq)), eps);
   const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
   const long long n4 = numel >> 2;
   for (long long i = tid; i < n4; i += nthreads) {
     float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c.nesterov || c.l2 != 0.0f) gv = __ldg(reinterpret_cast<const float4*>(g) + i);
+    if (c.nesterov) gv = __ldg(reinterpret_cast<const float4*>(g) + i);
     if (c.nesterov && c.l2 != 0.0f) {
       const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
       gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
@@ -248,32 +247,116 @@ __global__ void __launch_bounds__(kEwThreads)
     reinterpret_cast<uint2*>(out)[i] = t;
   }
   for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
-    float gv = g[i];
-    if (c.l2 != 0.0f) gv += c.l2 * p[i];
+    float gv = 0.f;
+    if (c.nesterov) {
+      gv = g[i];
+      if (c.l2 != 0.0f) gv += c.l2 * p[i];
+    }
     out[i] = __float2bfloat16_rn(muon_update(gv, m[i], c) / norm);
   }
 }
 
 // Weight update: p <- (p + shrink * p) - lr * ((u * scale) * extra), the operation order of
 // `p.add_(p, alpha=shrink)` followed by `p.add_(u * scale * extra, alpha=-lr)`.
+__device__ __forceinline__ float muon_apply_one(float pv, float uv, float shrink, float scale, float extra, float lr) {
+  if (shrink != 0.0f) pv = pv + shrink * pv;
+  const float t = (uv * scale) * extra;
+  return pv + (-lr) * t;
+}
+
 template <typename U>
-__global__ void __launch_bounds__(kEwThreads)
-    muon_apply_kernel(float* __restrict__ p, const U* __restrict__ u, long long numel, float shrink, float scale,
-                      float extra, float lr) {
+__device__ __forceinline__ void muon_apply_body(float* __restrict__ p, const U* __restrict__ u, long long numel,
+                                                float shrink, float scale, float extra, float lr) {
   const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
-  for (long long i = tid; i < numel; i += nthreads) {
-    float pv = p[i];
-    if (shrink != 0.0f) pv = pv + shrink * pv;
+  const bool vec = (reinterpret_cast<uintptr_t>(p) % 16 == 0) && (reinterpret_cast<uintptr_t>(u) % (4 * sizeof(U)) == 0);
+  const long long n4 = vec ? (numel >> 2) : 0;
+  for (long long i = tid; i < n4; i += nthreads) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    float u0, u1, u2, u3;
+    if constexpr (sizeof(U) == 2) {
+      const uint2 t = __ldg(reinterpret_cast<const uint2*>(u) + i);
+      u0 = __uint_as_float(t.x << 16); u1 = __uint_as_float(t.x & 0xFFFF0000u);
+      u2 = __uint_as_float(t.y << 16); u3 = __uint_as_float(t.y & 0xFFFF0000u);
+    } else {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(u) + i);
+      u0 = t.x; u1 = t.y; u2 = t.z; u3 = t.w;
+    }
+    pv.x = muon_apply_one(pv.x, u0, shrink, scale, extra, lr);
+    pv.y = muon_apply_one(pv.y, u1, shrink, scale, extra, lr);
+    pv.z = muon_apply_one(pv.z, u2, shrink, scale, extra, lr);
+    pv.w = muon_apply_one(pv.w, u3, shrink, scale, extra, lr);
+    reinterpret_cast<float4*>(p)[i] = pv;
+  }
+  for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
     float uv;
     if constexpr (sizeof(U) == 2) {
       uv = __bfloat162float(u[i]);
     } else {
       uv = u[i];
     }
-    const float t = (uv * scale) * extra;
-    p[i] = pv + (-lr) * t;
+    p[i] = muon_apply_one(p[i], uv, shrink, scale, extra, lr);
   }
+}
+
+__global__ void __launch_bounds__(kEwThreads)
+    muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ m, const float* __restrict__ p,
+                         long long numel, MuonEw c, double* __restrict__ partial) {
+  muon_momentum_body(g, m, p, numel, c, partial + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(kEwThreads)
+    muon_normalize_kernel(const float* __restrict__ g, const float* __restrict__ m, const float* __restrict__ p,
+                          long long numel, MuonEw c, const double* __restrict__ sumsq, float eps,
+                          __nv_bfloat16* __restrict__ out) {
+  muon_normalize_body(g, m, p, numel, c, sumsq[0], eps, out);
+}
+
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads)
+    muon_apply_kernel(float* __restrict__ p, const U* __restrict__ u, long long numel, float shrink, float scale,
+                      float extra, float lr) {
+  muon_apply_body<U>(p, u, numel, shrink, scale, extra, lr);
+}
+
+// Multi-tensor variants: blockIdx.y selects a tensor from a table passed by value in the kernel parameters
+// (no device-side table, no host-to-device copy); blockIdx.x partitions that tensor as the single-tensor
+// kernels do, so results are bit-identical to theirs.
+constexpr int kMtMax = 48;
+
+struct MtPrepare {
+  const float* g[kMtMax];
+  float* m[kMtMax];
+  const float* p[kMtMax];
+};
+
+struct MtApply {
+  float* p[kMtMax];
+  const void* u[kMtMax];
+  long long numel[kMtMax];
+  float scale[kMtMax];
+};
+
+__global__ void __launch_bounds__(kEwThreads)
+    muon_momentum_mt_kernel(const __grid_constant__ MtPrepare t, long long numel, MuonEw c,
+                            double* __restrict__ partial) {
+  const int y = blockIdx.y;
+  muon_momentum_body(t.g[y], t.m[y], t.p[y], numel, c, partial + static_cast<long long>(y) * gridDim.x + blockIdx.x);
+}
+
+__global__ void __launch_bounds__(kEwThreads)
+    muon_normalize_mt_kernel(const __grid_constant__ MtPrepare t, long long numel, MuonEw c,
+                             const double* __restrict__ sumsq, float eps, __nv_bfloat16* __restrict__ out,
+                             long long slot_stride) {
+  const int y = blockIdx.y;
+  muon_normalize_body(t.g[y], t.m[y], t.p[y], numel, c, sumsq[y], eps, out + static_cast<long long>(y) * slot_stride);
+}
+
+template <typename U>
+__global__ void __launch_bounds__(kEwThreads)
+    muon_apply_mt_kernel(const __grid_constant__ MtApply t, float shrink, float extra, float lr) {
+  const int y = blockIdx.y;
+  muon_apply_body<U>(t.p[y], static_cast<const U*>(t.u[y]), t.numel[y], shrink, t.scale[y], extra, lr);
 }
 
 inline int ew_blocks(long long numel, int per_thread) {

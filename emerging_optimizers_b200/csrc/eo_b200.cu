@@ -381,6 +381,193 @@ int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t 
   return EO_OK;
 }
 
+size_t eo_muon_prepare_scratch_bytes(int n, int64_t numel) {
+  if (n <= 0 || numel <= 0) return 0;
+  return static_cast<size_t>(n) * eo::sumsq_blocks_per_matrix(numel, 1) * sizeof(double);
+}
+
+int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const float* const* p, int64_t numel,
+                          double momentum, int nesterov, float l2_weight_decay, float eps, void* out_stack,
+                          int64_t slot_stride, double* sumsq, void* scratch, size_t scratch_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (n < 0 || numel < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (n == 0 || numel == 0) return EO_OK;
+  if (g == nullptr || m == nullptr || out_stack == nullptr || sumsq == nullptr)
+    return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (l2_weight_decay != 0.0f && p == nullptr) return fail(EO_ERR_BAD_ARG, "l2 weight decay needs p");
+  if (slot_stride < numel || slot_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(out_stack) & 15))
+    return fail(EO_ERR_BAD_ARG, "out_stack must be 16-byte aligned with a slot stride >= numel that is a multiple of 8");
+  const size_t need = eo_muon_prepare_scratch_bytes(n, numel);
+  if (scratch_bytes < need || scratch == nullptr)
+    return fail(EO_ERR_WORKSPACE, "muon prepare scratch: need %zu bytes, got %zu", need, scratch_bytes);
+  for (int i = 0; i < n; ++i) {
+    uintptr_t bits = reinterpret_cast<uintptr_t>(g[i]) | reinterpret_cast<uintptr_t>(m[i]);
+    if (p != nullptr) bits |= reinterpret_cast<uintptr_t>(p[i]);
+    if (g[i] == nullptr || m[i] == nullptr || (bits & 15))
+      return fail(EO_ERR_BAD_ARG, "tensor %d: g, m and p must be non-null and 16-byte aligned", i);
+  }
+  const int nblk = eo::sumsq_blocks_per_matrix(numel, 1);
+  const eo::MuonEw c{static_cast<float>(momentum), static_cast<float>(1.0 - momentum), l2_weight_decay,
+                     nesterov ? 1 : 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  double* partial = static_cast<double*>(scratch);
+  for (int i0 = 0; i0 < n; i0 += eo::kMtMax) {
+    const int cnt = (n - i0 < eo::kMtMax) ? (n - i0) : eo::kMtMax;
+    eo::MtPrepare t;
+    memset(&t, 0, sizeof(t));
+    for (int i = 0; i < cnt; ++i) {
+      t.g[i] = g[i0 + i];
+      t.m[i] = m[i0 + i];
+      t.p[i] = (p != nullptr) ? p[i0 + i] : nullptr;
+    }
+    eo::muon_momentum_mt_kernel<<<dim3(nblk, cnt), eo::kEwThreads, 0, s>>>(t, numel, c,
+                                                                          partial + static_cast<int64_t>(i0) * nblk);
+    eo::sumsq_final_kernel<<<cnt, eo::kEwThreads, 0, s>>>(partial + static_cast<int64_t>(i0) * nblk, nblk, sumsq + i0);
+    eo::muon_normalize_mt_kernel<<<dim3(eo::ew_blocks(numel, 16), cnt), eo::kEwThreads, 0, s>>>(
+        t, numel, c, sumsq + i0, eps, static_cast<__nv_bfloat16*>(out_stack) + static_cast<int64_t>(i0) * slot_stride,
+        slot_stride);
+  }
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int update_is_bf16, const int64_t* numel,
+                        const float* scale, float shrink, float extra_scale, float lr, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (n < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (n == 0) return EO_OK;
+  if (p == nullptr || update == nullptr || numel == nullptr || scale == nullptr)
+    return fail(EO_ERR_BAD_ARG, "null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i0 = 0; i0 < n; i0 += eo::kMtMax) {
+    const int cnt = (n - i0 < eo::kMtMax) ? (n - i0) : eo::kMtMax;
+    eo::MtApply t;
+    memset(&t, 0, sizeof(t));
+    int64_t biggest = 0;
+    for (int i = 0; i < cnt; ++i) {
+      if (p[i0 + i] == nullptr || update[i0 + i] == nullptr || numel[i0 + i] < 0)
+        return fail(EO_ERR_BAD_ARG, "tensor %d: null pointer or negative size", i0 + i);
+      t.p[i] = p[i0 + i];
+      t.u[i] = update[i0 + i];
+      t.numel[i] = numel[i0 + i];
+      t.scale[i] = scale[i0 + i];
+      if (numel[i0 + i] > biggest) biggest = numel[i0 + i];
+    }
+    const dim3 grid(eo::ew_blocks(biggest, 16), cnt);
+    if (update_is_bf16)
+      eo::muon_apply_mt_kernel<__nv_bfloat16><<<grid, eo::kEwThreads, 0, s>>>(t, shrink, extra_scale, lr);
+    else
+      eo::muon_apply_mt_kernel<float><<<grid, eo::kEwThreads, 0, s>>>(t, shrink, extra_scale, lr);
+  }
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+namespace {
+inline int64_t round_up(int64_t v, int64_t to) { return (v + to - 1) / to * to; }
+
+struct NsLayout {
+  int m, n;           // Gram side and contraction length of the wide orientation
+  int64_t ldm;        // row stride of A and B
+  int64_t a_elems;    // elements of one of A / B (whole batch)
+  int64_t ldt;        // row stride of the temporary iterate
+  int64_t t_stride;   // batch stride of the temporary iterate
+  int64_t t_elems;
+};
+
+NsLayout ns_layout(int batch, int rows, int cols) {
+  NsLayout L;
+  L.m = rows <= cols ? rows : cols;
+  L.n = rows <= cols ? cols : rows;
+  L.ldm = round_up(L.m, 8);
+  L.a_elems = round_up(static_cast<int64_t>(batch) * L.m * L.ldm, 128);
+  L.ldt = round_up(cols, 8);
+  L.t_stride = round_up(static_cast<int64_t>(rows) * L.ldt, 8);
+  L.t_elems = round_up(static_cast<int64_t>(batch) * L.t_stride, 128);
+  return L;
+}
+}  // namespace
+
+size_t eo_newton_schulz_workspace_bytes(int batch, int rows, int cols) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+  const NsLayout L = ns_layout(batch, rows, cols);
+  return static_cast<size_t>(2 * L.a_elems + L.t_elems) * 2;
+}
+
+int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
+                          int steps, int use_syrk, void* out, int out_fp32, int64_t ldo, int64_t strideo,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0 || steps < 1) return fail(EO_ERR_BAD_ARG, "bad size or steps < 1");
+  if (batch == 0 || rows == 0 || cols == 0) return EO_OK;
+  if (X == nullptr || out == nullptr || host_abc == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  const size_t need = eo_newton_schulz_workspace_bytes(batch, rows, cols);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(EO_ERR_WORKSPACE, "newton_schulz workspace: need %zu bytes, got %zu", need, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(EO_ERR_BAD_ARG, "workspace must be 256-byte aligned");
+  const NsLayout L = ns_layout(batch, rows, cols);
+  const bool tall = rows > cols;
+  char* ws = static_cast<char*>(workspace);
+  void* A = ws;
+  void* S = ws + L.a_elems * 2;
+  void* T = ws + 2 * L.a_elems * 2;
+  const int64_t a_stride = static_cast<int64_t>(L.m) * L.ldm;
+  const int syrk = use_syrk && (rows % 8 == 0) && (cols % 8 == 0);
+
+  // Iterate buffers: step i reads `cur` and writes `nxt`; the last step writes `out`.
+  void* cur = X;
+  int64_t cur_ld = ld, cur_stride = stride;
+  for (int it = 0; it < steps; ++it) {
+    const float a = host_abc[3 * it], b = host_abc[3 * it + 1], c = host_abc[3 * it + 2];
+    const bool last = (it == steps - 1);
+    int rc;
+    // A = X X^T over the wide orientation.  Wide storage: operands K-major; tall storage: MN-major.
+    rc = launch_gemm(cur, tall ? 1 : 0, cur_ld, cur_stride, 0, cur, tall ? 1 : 0, cur_ld, cur_stride, 0, nullptr, 0, 0,
+                     A, L.ldm, a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 0, 0, 0, syrk, 0, stream);
+    if (rc) return rc;
+    const void* Sop = A;
+    float alpha = b, beta = a;
+    if (c != 0.0f) {
+      // S = b A + c A A (A symmetric)
+      rc = launch_gemm(A, 0, L.ldm, a_stride, 0, A, syrk ? 0 : 1, L.ldm, a_stride, 0, A, L.ldm, a_stride, S, L.ldm,
+                       a_stride, batch, L.m, L.m, L.m, c, b, 1.0f, 0, 0, 0, syrk, 0, stream);
+      if (rc) return rc;
+      Sop = S;
+      alpha = 1.0f;
+    }
+    void* dst;
+    int64_t dst_ld, dst_stride;
+    if (last) {
+      dst = out;
+      dst_ld = ldo;
+      dst_stride = strideo;
+    } else {
+      // ping-pong between the temporary and the caller's X (which is clobbered from the second step on)
+      dst = (cur == X) ? T : X;
+      dst_ld = (dst == T) ? L.ldt : ld;
+      dst_stride = (dst == T) ? L.t_stride : stride;
+    }
+    const int d32 = last ? out_fp32 : 0;
+    if (!tall) {
+      // X' = beta X + alpha S X : A-operand S (m x m, K-major), B-operand X as (n x m): stored m x n, MN-major
+      rc = launch_gemm(Sop, 0, L.ldm, a_stride, 0, cur, 1, cur_ld, cur_stride, 0, cur, cur_ld, cur_stride, dst, dst_ld,
+                       dst_stride, batch, L.m, L.n, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream);
+    } else {
+      // stored transposed (n x m): X'^T = beta X^T + alpha X^T S, S symmetric, both operands K-major
+      rc = launch_gemm(cur, 0, cur_ld, cur_stride, 0, Sop, 0, L.ldm, a_stride, 0, cur, cur_ld, cur_stride, dst, dst_ld,
+                       dst_stride, batch, L.n, L.m, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream);
+    }
+    if (rc) return rc;
+    cur = dst;
+    cur_ld = dst_ld;
+    cur_stride = dst_stride;
+  }
+  return EO_OK;
+}
+
 size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }
 
 int eo_sumsq_f32_noalloc(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,

@@ -234,15 +234,23 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         if self.world == 1:
             for b in self.buckets:
                 idxs = [i for i, _ in b.per_rank[0]]
-                for i, orth in self._orthogonalize_many(idxs, fused).items():
-                    self._apply(i, orth, fused)
+                orths = self._orthogonalize_many(idxs, fused)
+                if fused:
+                    scales = [get_muon_scale_factor(*self.params[i].shape[-2:], mode=self.scale_mode) for i in idxs]
+                    shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay else 0.0
+                    _native.muon_apply_batch(
+                        [self.params[i].data for i in idxs], [orths[i] for i in idxs], scales, shrink,
+                        self.extra_scale_factor, self.lr,
+                    )
+                else:
+                    for i in idxs:
+                        self._apply(i, orths[i], fused)
             return
 
         dev = self.params[0].device
         on_gpu = dev.type == "cuda"
         if on_gpu and self._side is None:
             self._side = torch.cuda.Stream(device=dev)
-        pending = []
         for b in self.buckets:
             slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
             mine = b.per_rank[self.rank]
@@ -251,27 +259,40 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
                 slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
             gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
             if on_gpu:
+                # Exchange and weight update of this bucket run on the side stream, behind the Newton-Schulz work
+                # of the following buckets: the update is HBM-bound, the iteration tensor-bound.
                 ready = torch.cuda.Event()
                 ready.record()
                 with torch.cuda.stream(self._side):
                     self._side.wait_event(ready)
                     dist.all_gather_into_tensor(gathered, slot, group=self.group)
-                    done = torch.cuda.Event()
-                    done.record()
+                    self._apply_bucket(b, gathered, fused)
                 slot.record_stream(self._side)
                 gathered.record_stream(self._side)
             else:
                 dist.all_gather_into_tensor(gathered, slot, group=self.group)
-                done = None
-            pending.append((b, gathered, done))
-        for b, gathered, done in pending:
-            if done is not None:
-                torch.cuda.current_stream().wait_event(done)
+                self._apply_bucket(b, gathered, fused)
+        if on_gpu:
+            torch.cuda.current_stream().wait_stream(self._side)
+
+    def _apply_bucket(self, b: _Bucket, gathered: torch.Tensor, fused: bool) -> None:
+        if fused:
+            ps, us, scales = [], [], []
             for r in range(self.world):
                 base = r * b.slot_numel
                 for i, off in b.per_rank[r]:
                     p = self.params[i]
-                    self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p), fused)
+                    ps.append(p.data)
+                    us.append(gathered[base + off : base + off + p.numel()])
+                    scales.append(get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode))
+            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
+            _native.muon_apply_batch(ps, us, scales, shrink, self.extra_scale_factor, self.lr)
+            return
+        for r in range(self.world):
+            base = r * b.slot_numel
+            for i, off in b.per_rank[r]:
+                p = self.params[i]
+                self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p), fused)
 
     # -- checkpointing -----------------------------------------------------------------------------------
     def state_dict(self) -> dict:

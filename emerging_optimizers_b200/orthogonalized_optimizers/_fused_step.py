@@ -86,24 +86,26 @@ def orthogonalized_updates(
     schedule = list(muon_utils.get_coefficient_iterator(steps, sets, mode=mode))
 
     out: list[torch.Tensor | None] = [None] * len(params)
-    syrk_ok = use_syrk
     for batch in plan_batches([tuple(p.shape) for p in params], max_batch_bytes):
         rows, cols = params[batch[0]].shape
         dev = params[batch[0]].device
-        stack = torch.empty((len(batch), rows, cols), dtype=torch.bfloat16, device=dev)
-        for slot, i in enumerate(batch):
-            ss = _native.muon_momentum(grads[i], momenta[i], params[i], momentum, nesterov, l2_weight_decay)
-            _native.muon_normalize(
-                grads[i], momenta[i], params[i], momentum, nesterov, l2_weight_decay, ss, eps, stack[slot]
-            )
-        # Iterate on the wide orientation; a tall matrix is used through its transposed view (no copy).
-        X = stack.mT if rows > cols else stack
-        syrk = syrk_ok and rows % 8 == 0 and cols % 8 == 0
-        for a, b, c in schedule:
-            X = muon_utils._ns_step(X, a, b, c, None, use_syrk=syrk)
-        X = X.mT if rows > cols else X
-        if not X.is_contiguous():
+        # Row stride padded to 16 bytes so that TMA can address shapes like 40 x 24 too.
+        ld = (cols + 7) // 8 * 8
+        slot = (rows * ld + 7) // 8 * 8
+        gs, ms, ps = [grads[i] for i in batch], [momenta[i] for i in batch], [params[i] for i in batch]
+        stack = torch.empty((len(batch), slot), dtype=torch.bfloat16, device=dev)
+        if ld == cols:
+            _native.muon_prepare_batch(gs, ms, ps, momentum, nesterov, l2_weight_decay, eps, stack)
+            X = stack[:, : rows * cols].unflatten(1, (rows, cols))
+        else:
+            dense = torch.empty((len(batch), (rows * cols + 7) // 8 * 8), dtype=torch.bfloat16, device=dev)
+            _native.muon_prepare_batch(gs, ms, ps, momentum, nesterov, l2_weight_decay, eps, dense)
+            X = stack[:, : rows * ld].unflatten(1, (rows, ld))[:, :, :cols]
+            X.copy_(dense[:, : rows * cols].unflatten(1, (rows, cols)))
+        if schedule:
+            X = _native.newton_schulz_bf16(X, schedule, use_syrk)
+        elif not X.is_contiguous():
             X = X.contiguous()
-        for slot, i in enumerate(batch):
-            out[i] = X[slot]
+        for k, i in enumerate(batch):
+            out[i] = X[k]
     return out  # type: ignore[return-value]

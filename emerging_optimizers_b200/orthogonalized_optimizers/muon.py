@@ -200,9 +200,8 @@ class Muon(OrthogonalizedOptimizer[HookStateT]):
                 use_syrk=self._use_syrk,
             )
             shrink = _SHRINK[self.weight_decay_method](lr, wd) if wd != 0.0 else 0.0
-            for p, u in zip(fused, updates):
-                scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self._scale_mode)
-                _native.muon_apply(p.data, u, shrink, scale, self._extra_scale_factor, lr)
+            scales = [get_muon_scale_factor(p.size(-2), p.size(-1), mode=self._scale_mode) for p in fused]
+            _native.muon_apply_batch([p.data for p in fused], updates, scales, shrink, self._extra_scale_factor, lr)
         return None
 
     num_ns_steps = _read_only("num_ns_steps")

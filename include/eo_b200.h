@@ -194,6 +194,47 @@ int eo_muon_normalize_bf16(const float* g, const float* m, const float* p, int64
 int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t numel, float shrink, float scale,
                       float extra_scale, float lr, void* stream);
 
+/*
+ * Multi-tensor forms of the three calls above for a group of parameters (host arrays of device
+ * pointers; the tables travel in kernel parameters, nothing is copied to the device).
+ *
+ *   eo_muon_prepare_batch: for n tensors of the same `numel`: momentum update, sum of squares
+ *       (sumsq[i], device double[n]) and the normalised bf16 tensor written to
+ *       out_stack + i * slot_stride - the stacked (n, rows, cols) input of a batched Newton-Schulz run.
+ *       `p` may be NULL when l2_weight_decay == 0.  scratch: eo_muon_prepare_scratch_bytes(n, numel).
+ *   eo_muon_apply_batch  : weight update of n tensors of any sizes; update[i] is bf16 or fp32 for all i.
+ *
+ * Results are bit-identical to the single-tensor calls.
+ */
+size_t eo_muon_prepare_scratch_bytes(int n, int64_t numel);
+int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const float* const* p, int64_t numel,
+                          double momentum, int nesterov, float l2_weight_decay, float eps, void* out_stack,
+                          int64_t slot_stride, double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
+int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int update_is_bf16, const int64_t* numel,
+                        const float* scale, float shrink, float extra_scale, float lr, void* stream);
+
+/*
+ * The whole iteration loop of newton_schulz on the bf16 path in one call:
+ *
+ *     for (a, b, c) in host_abc[0 .. steps):  A = X X^T;  S = b A + c A A  (skipped if c == 0);
+ *                                             X <- a X + S X   (a X + b A X if c == 0)
+ *
+ * X is the normalised bf16 iterate, (batch, rows, cols) row-major with leading dimension `ld` and batch
+ * stride `stride` (multiples of 8, 16-byte-aligned base); the iteration runs on the wide orientation
+ * (on X^T, without copying, when rows > cols).  The last step writes `out` (bf16, or fp32 = bf16-rounded
+ * values widened, with ldo / strideo); X is used as a ping-pong buffer and is clobbered when steps > 1.
+ * `use_syrk` selects the lower-triangular kernel for A and S (falls back to the general kernel when
+ * rows or cols is not a multiple of 8).  `host_abc` is a host array of 3 * steps floats.
+ * `workspace`: eo_newton_schulz_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
+ *
+ * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 with
+ * the step functions of :348-476; launches 3 * steps (2 * steps when c == 0) kernels.
+ */
+size_t eo_newton_schulz_workspace_bytes(int batch, int rows, int cols);
+int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
+                          int steps, int use_syrk, void* out, int out_fp32, int64_t ldo, int64_t strideo,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -173,6 +173,27 @@ def test_replaced_step_function_is_used():
         assert torch.equal(y, muon_utils.newton_schulz(x, 3, "simple", use_syrk=True))
 
 
+@pytest.mark.parametrize("shape", [(256, 640), (640, 256), (3, 128, 384), (2, 384, 128), (256, 256)])
+@pytest.mark.parametrize("ctype,steps", [("quintic", 5), ("cubic5", 5), ("polar_express", 1)])
+def test_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
+    """The one-call iteration loop of the library against the same kernels driven step by step from Python
+    (selected here by wrapping a step function, which is how a caller opts out of the single call)."""
+    x = randn_tensor(*shape, seed=40)
+    names = ["newton_schulz_step", "batched_newton_schulz_step", "newton_schulz_step_tsyrk", "batched_newton_schulz_step_tsyrk"]
+    for use_syrk in (False, True):
+        with fp32_matmul_precision("medium"):
+            fast = muon_utils.newton_schulz(x, steps, ctype, use_syrk=use_syrk)
+            saved = {n: getattr(muon_utils, n) for n in names}
+            try:
+                for n, fn in saved.items():
+                    setattr(muon_utils, n, (lambda f: lambda X, a, b, c, tp_group=None: f(X, a, b, c, tp_group=tp_group))(fn))
+                slow = muon_utils.newton_schulz(x, steps, ctype, use_syrk=use_syrk)
+            finally:
+                for n, fn in saved.items():
+                    setattr(muon_utils, n, fn)
+        assert fast.shape == slow.shape and torch.equal(fast, slow)
+
+
 def test_muon_steps_match_reference_golden(golden_dir):
     data = np.load(os.path.join(golden_dir, "muon_steps.npz"))
     with open(os.path.join(golden_dir, "muon_cases.json")) as f:
