@@ -14,8 +14,10 @@ Design for one NVSwitch box (one process per GPU, NCCL through ``torch.distribut
 - The owner keeps the momentum buffer of a matrix (1/P of the optimizer state per rank), updates it, applies
   Nesterov and runs Newton-Schulz.  On the bf16 path the Newton-Schulz result is bf16-valued, so it is exchanged
   as bf16 without loss: 2 bytes per parameter cross NVLink instead of 4.
-- The exchange is one ``all_gather_into_tensor`` per bucket of matrices, issued on a side stream as soon as the
-  bucket's matrices are done, so it overlaps the Newton-Schulz work of the next bucket.
+- The exchange is one all-gather per bucket of matrices, issued on a side stream as soon as the bucket's matrices
+  are done, so it overlaps the Newton-Schulz work of the next bucket.  On GPUs it is made of copy-engine pushes
+  into the peers' symmetric buffers plus a group barrier (no SM is taken from the persistent tensor-core
+  kernels); host ranks (gloo, used by the tests) call ``all_gather_into_tensor``.
 - Weight decay and ``p -= lr * scale * update`` are then applied by every rank to every matrix with the same fp32
   arithmetic, which makes the parameters bitwise identical across ranks and equal to the single-process result.
 """
@@ -155,6 +157,8 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel)
         self.state: dict[int, dict[str, torch.Tensor]] = {}
         self._side: "torch.cuda.Stream | None" = None
+        self._peer = None  # symmetric exchange buffer, created collectively at the first multi-GPU step
+        self._exchanges = 0
 
     # -- pieces of the step ------------------------------------------------------------------------------
     def owned_indices(self) -> list[int]:
@@ -248,32 +252,48 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             return
 
         dev = self.params[0].device
-        on_gpu = dev.type == "cuda"
-        if on_gpu and self._side is None:
-            self._side = torch.cuda.Stream(device=dev)
-        for b in self.buckets:
-            slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
-            mine = b.per_rank[self.rank]
-            orths = self._orthogonalize_many([i for i, _ in mine], fused)
-            for i, off in mine:
-                slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
-            gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
-            if on_gpu:
-                # Exchange and weight update of this bucket run on the side stream, behind the Newton-Schulz work
-                # of the following buckets: the update is HBM-bound, the iteration tensor-bound.
-                ready = torch.cuda.Event()
-                ready.record()
-                with torch.cuda.stream(self._side):
-                    self._side.wait_event(ready)
-                    dist.all_gather_into_tensor(gathered, slot, group=self.group)
-                    self._apply_bucket(b, gathered, fused)
-                slot.record_stream(self._side)
-                gathered.record_stream(self._side)
-            else:
+        if dev.type != "cuda":
+            # Host ranks (tests on gloo): plain collective, no overlap.
+            for b in self.buckets:
+                slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
+                mine = b.per_rank[self.rank]
+                orths = self._orthogonalize_many([i for i, _ in mine], fused)
+                for i, off in mine:
+                    slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
+                gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
                 dist.all_gather_into_tensor(gathered, slot, group=self.group)
                 self._apply_bucket(b, gathered, fused)
-        if on_gpu:
-            torch.cuda.current_stream().wait_stream(self._side)
+            return
+
+        # GPU ranks: the exchange of bucket j (copy-engine pushes into the peers' symmetric buffers, a group
+        # barrier) and its weight update run on a side stream behind the Newton-Schulz work of bucket j + 1.
+        # The copies use no SM and the update is HBM-bound while the iteration is tensor-bound.  The symmetric
+        # buffer has two halves used alternately; a half is rewritten only after the barrier of the exchange in
+        # between, which every rank enters after it has consumed that half.
+        max_slot = max(b.slot_numel for b in self.buckets)
+        if self._peer is None:
+            from emerging_optimizers_b200.distributed.peer_memory import PeerBuffer
+
+            self._side = torch.cuda.Stream(device=dev)
+            self._peer = PeerBuffer(2 * self.world * max_slot, self.exchange_dtype, dev, self.group)
+            self._exchanges = 0
+        peer, side = self._peer, self._side
+        for b in self.buckets:
+            mine = b.per_rank[self.rank]
+            orths = self._orthogonalize_many([i for i, _ in mine], fused)
+            base = (self._exchanges % 2) * self.world * max_slot
+            self._exchanges += 1
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                own = base + self.rank * b.slot_numel
+                for i, off in mine:
+                    peer.local[own + off : own + off + orths[i].numel()].copy_(orths[i].reshape(-1))
+                    orths[i].record_stream(side)
+                peer.all_gather_slots(base, b.slot_numel)
+                self._apply_bucket(b, peer.local[base : base + self.world * b.slot_numel], fused)
+        torch.cuda.current_stream().wait_stream(side)
 
     def _apply_bucket(self, b: _Bucket, gathered: torch.Tensor, fused: bool) -> None:
         if fused:

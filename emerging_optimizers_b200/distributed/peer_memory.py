@@ -1,0 +1,72 @@
+"""Peer-visible device buffers inside one NVSwitch box and collectives built on them.
+
+``torch.distributed._symmetric_memory`` allocates a buffer on every rank of a group and maps all of them into
+every rank's address space (CUDA virtual-memory handles exchanged over the process group), so a rank can write a
+peer's buffer with an ordinary device-to-device copy or an ordinary store from a kernel.  Two uses here:
+
+- :meth:`PeerBuffer.all_gather_slots`: an all-gather made of copy-engine transfers (one ``cudaMemcpyAsync`` per
+  peer, on its own stream) followed by a group barrier.  It occupies no SM, so it does not take SMs away from the
+  persistent tensor-core kernels it overlaps with, which a kernel-based collective does.
+- the raw peer pointers (:attr:`PeerBuffer.ptrs`) handed to kernels that store to peers directly.
+
+Only plain copies, plain loads/stores and the library's own barrier touch peer memory; no TMA load with cluster
+multicast ever reads it.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+__all__ = ["PeerBuffer"]
+
+
+class PeerBuffer:
+    """A symmetric buffer of ``numel`` elements of ``dtype`` on every rank of ``group``.
+
+    Must be constructed collectively (every rank, same arguments, same order).
+    """
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, group: "dist.ProcessGroup | None" = None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.numel, self.dtype, self.device = numel, dtype, device
+        self.local = symm.empty(numel, dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.local, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._copy_streams = [torch.cuda.Stream(device=device) for _ in range(max(self.world - 1, 1))]
+
+    def peer_view(self, peer: int, numel: int, offset: int = 0) -> torch.Tensor:
+        """``numel`` elements of rank ``peer``'s buffer starting at element ``offset``, as a local tensor."""
+        if peer == self.rank:
+            return self.local[offset : offset + numel]
+        return self.handle.get_buffer(peer, (numel,), self.dtype, offset)
+
+    def barrier(self) -> None:
+        """Group barrier enqueued on the current stream (every rank's stream passes it together)."""
+        self.handle.barrier(channel=0)
+
+    def all_gather_slots(self, base: int, slot_numel: int) -> None:
+        """All-gather in place: region ``base + r * slot_numel`` holds rank r's slot on every rank afterwards.
+
+        The caller has filled its own slot of its own buffer.  Enqueued on the current stream: the slot is pushed
+        to every peer by copy engines (parallel streams), then the group barrier orders the arrival of all pushes
+        before anything enqueued after this call.
+        """
+        cur = torch.cuda.current_stream(self.device)
+        mine = base + self.rank * slot_numel
+        src = self.local[mine : mine + slot_numel]
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        for k in range(1, self.world):
+            peer = (self.rank + k) % self.world
+            s = self._copy_streams[k - 1]
+            with torch.cuda.stream(s):
+                s.wait_event(ready)
+                self.peer_view(peer, slot_numel, mine).copy_(src, non_blocking=True)
+            cur.wait_stream(s)
+        self.barrier()
