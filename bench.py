@@ -123,7 +123,8 @@ def workload_config(n_gpus: int) -> dict:
         "workload": f"newton_schulz {M}x{N_COLS} fp32 in/out, {NS_STEPS} '{COEFF}' steps, bf16 tensor-core path "
         "(fp32 matmul precision 'medium', use_syrk=True)",
         "matrices_per_step": n_gpus,
-        "parallelism": "single device" if n_gpus == 1 else f"layer-parallel x{n_gpus}: one matrix per rank, all-gather of results",
+        "parallelism": "single device" if n_gpus == 1 else f"layer-parallel x{n_gpus}: one matrix per rank, all-gather of "
+        "the bf16 results by copy-engine pushes into symmetric memory, overlapped with the next call",
         "l2": "inputs larger than L2 (940 MB fp32 input, 470 MB bf16 iterate per matrix)",
         "flop_convention": "value: dense-equivalent 4m^2n+2m^3 per iteration; roofline: symmetric outputs counted once",
     }
@@ -221,8 +222,21 @@ def run_gpu_arm(args) -> None:
     x = x_host.to(dev, non_blocking=True)
     torch.cuda.synchronize()
 
-    gather_buf = torch.empty(world, M, N_COLS, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    # Exchange buffer of the layer-parallel scheme: symmetric memory written by copy engines (no SMs taken from the
+    # persistent tensor-core kernels); NCCL all-gather if symmetric memory cannot be set up on this box.
     side = torch.cuda.Stream(device=dev)
+    gather_buf, peer = None, None
+    slot = M * N_COLS
+    if world > 1:
+        try:
+            from emerging_optimizers_b200.distributed.peer_memory import PeerBuffer
+
+            peer = PeerBuffer(2 * world * slot, torch.bfloat16, dev)
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(f"symmetric memory unavailable ({exc}); using NCCL all-gather", file=sys.stderr)
+            gather_buf = torch.empty(world, M, N_COLS, dtype=torch.bfloat16, device=dev)
+    exchanges = [0]
 
     def ns_call(inp: torch.Tensor) -> torch.Tensor:
         with fp32_matmul_precision("medium"):
@@ -232,13 +246,19 @@ def run_gpu_arm(args) -> None:
         y = ns_call(x)
         if world > 1:
             # exchange step of the layer-parallel scheme, overlapped with the next call on a side stream
-            yb = y.to(torch.bfloat16)
             ev = torch.cuda.Event()
             ev.record()
             with torch.cuda.stream(side):
                 side.wait_event(ev)
-                dist.all_gather_into_tensor(gather_buf.view(-1), yb.view(-1))
-                yb.record_stream(side)
+                if peer is not None:
+                    base = (exchanges[0] % 2) * world * slot
+                    exchanges[0] += 1
+                    peer.local[base + rank * slot : base + (rank + 1) * slot].copy_(y.view(-1))  # fp32 -> bf16, lossless
+                    peer.all_gather_slots(base, slot)
+                else:
+                    yb = y.to(torch.bfloat16)
+                    dist.all_gather_into_tensor(gather_buf.view(-1), yb.view(-1))
+                y.record_stream(side)
         return y
 
     n_warm = args.warmup if args.kernels_only else max(args.warmup, 3)

@@ -79,7 +79,7 @@ _PROTOTYPES: dict[str, tuple] = {
     ),
     "eo_muon_apply_batch": (
         c_int,
-        [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p],
+        [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_int, c_void_p],
     ),
     "eo_newton_schulz_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "eo_newton_schulz_bf16": (
@@ -480,7 +480,9 @@ def muon_prepare_batch(
     return ss
 
 
-def muon_apply_batch(params, updates, scales, shrink: float, extra: float, lr: float) -> None:
+def muon_apply_batch(
+    params, updates, scales, shrink: float, extra: float, lr: float, max_blocks_per_tensor: int = 0
+) -> None:
     """Fused weight update of a list of contiguous fp32 parameters; ``updates`` all bf16 or all fp32."""
     n = len(params)
     if n == 0:
@@ -492,7 +494,7 @@ def muon_apply_batch(params, updates, scales, shrink: float, extra: float, lr: f
     with torch.cuda.device(dev), _Timed("muon_apply", (n + 47) // 48, dev):
         rc = lib().eo_muon_apply_batch(
             n, _ptr_array(params), _ptr_array(updates), 1 if is_bf16 else 0, numel, sc, shrink, extra, lr,
-            torch.cuda.current_stream(dev).cuda_stream,
+            max_blocks_per_tensor, torch.cuda.current_stream(dev).cuda_stream,
         )  # fmt: skip
     _check(rc, "eo_muon_apply_batch")
 

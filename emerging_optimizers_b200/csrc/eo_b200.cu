@@ -42,10 +42,18 @@ __device__ unsigned int g_device_status = 0;
 constexpr size_t kNoAllocMaxPartials = 65536;
 static __device__ __align__(256) double g_noalloc_partials[kNoAllocMaxPartials];
 
+// Tile-scheduler words of eo_gemm_kernel: kSchedSlots pairs {next tile, finished CTAs}, all zero between
+// launches.  Consecutive launches take consecutive slots, so kernels that overlap on different streams do not
+// share a pair unless more than kSchedSlots launches are in flight at once.
+constexpr int kSchedSlots = 1024;
+__device__ unsigned int g_sched_words[2 * kSchedSlots];
+
 struct DeviceInfo {
   bool ready = false;
   int sm_count = 0;
   unsigned int* status_ptr = nullptr;
+  unsigned int* sched_ptr = nullptr;
+  unsigned int sched_next = 0;
   double* noalloc_partials = nullptr;  // device address of g_noalloc_partials on this device
 };
 constexpr int kMaxDevices = 64;
@@ -68,6 +76,7 @@ int device_setup(DeviceInfo** out) {
     d.sm_count = prop.multiProcessorCount;
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_device_status));
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.noalloc_partials), g_noalloc_partials));
+    EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.sched_ptr), g_sched_words));
     EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
     if (g_encode == nullptr) {
@@ -232,6 +241,11 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   p.total_tiles = static_cast<int>(total);
   p.tiles_per_batch = p.total_tiles / batch;
 
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    p.sched = dev->sched_ptr + 2 * (dev->sched_next % kSchedSlots);
+    dev->sched_next++;
+  }
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
   eo::eo_gemm_kernel<<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
   EO_CUDA(cudaGetLastError());
@@ -433,7 +447,8 @@ int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const f
 }
 
 int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int update_is_bf16, const int64_t* numel,
-                        const float* scale, float shrink, float extra_scale, float lr, void* stream) {
+                        const float* scale, float shrink, float extra_scale, float lr, int max_blocks_per_tensor,
+                        void* stream) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (n < 0) return fail(EO_ERR_BAD_ARG, "negative size");
@@ -455,7 +470,9 @@ int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int u
       t.scale[i] = scale[i0 + i];
       if (numel[i0 + i] > biggest) biggest = numel[i0 + i];
     }
-    const dim3 grid(eo::ew_blocks(biggest, 16), cnt);
+    int bx = eo::ew_blocks(biggest, 16);
+    if (max_blocks_per_tensor > 0 && bx > max_blocks_per_tensor) bx = max_blocks_per_tensor;
+    const dim3 grid(bx, cnt);
     if (update_is_bf16)
       eo::muon_apply_mt_kernel<__nv_bfloat16><<<grid, eo::kEwThreads, 0, s>>>(t, shrink, extra_scale, lr);
     else

@@ -35,8 +35,10 @@ constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;  // row-block group height of the general tile order
 
-// Shared-memory budget: ring + barriers + TMEM address slot, plus slack for 1024-byte alignment.
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + 1024;
+constexpr int kTileQueue = 4;  // depth of the in-CTA queue of tile indices handed from the producer to the other roles
+
+// Shared-memory budget: ring + barriers + tile queue + TMEM address slot, plus slack for 1024-byte alignment.
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 512 + 1024;
 
 struct GemmParams {
   int batch, M, N, K;
@@ -62,6 +64,10 @@ struct GemmParams {
   //   lbo_*/sbo_*: leading / stride byte offsets of the operand's canonical 128B-swizzled layout
   unsigned int adv_a, adv_b, lbo_a, lbo_b, sbo_a, sbo_b;
   unsigned int* status;
+  // Work distribution: tiles are handed out through a global counter (`sched[0]`, next tile index), so a CTA
+  // that starts late or shares its SM with another kernel simply takes fewer tiles.  `sched[1]` counts CTAs that
+  // have finished; the last one zeroes both words for the next launch that uses this slot.
+  unsigned int* sched;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
@@ -224,7 +230,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* empty_bar = bars + kStages;          // [kStages]
   uint64_t* acc_full_bar = bars + 2 * kStages;   // [2]
   uint64_t* acc_empty_bar = acc_full_bar + 2;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty_bar + 2);
+  uint64_t* tq_full_bar = acc_empty_bar + 2;     // [kTileQueue]
+  uint64_t* tq_empty_bar = tq_full_bar + kTileQueue;  // [kTileQueue]
+  int* tile_queue = reinterpret_cast<int*>(tq_empty_bar + kTileQueue);  // [kTileQueue]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_queue + kTileQueue);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -237,6 +246,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
       mbar_init(&acc_empty_bar[s], 4);
+    }
+    for (int s = 0; s < kTileQueue; ++s) {
+      mbar_init(&tq_full_bar[s], 1);
+      mbar_init(&tq_empty_bar[s], 5);  // MMA thread + four epilogue warps
     }
     mbar_init_fence();
     for (int t = 0; t < p.nterms; ++t) {
@@ -263,8 +276,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
+      int tq = 0;
+      uint32_t tq_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      while (ok) {
+        // Take the next tile and publish it to the MMA and epilogue roles (-1: no tiles left).
+        int t = static_cast<int>(atomicAdd(p.sched, 1u));
+        if (t >= p.total_tiles) t = -1;
+        if (!mbar_wait(&tq_empty_bar[tq], tq_phase ^ 1u)) {
+          report(p, kStatusTimeoutProducer + 1u);
+          break;
+        }
+        tile_queue[tq] = t;
+        mbar_arrive(&tq_full_bar[tq]);
+        if (++tq == kTileQueue) {
+          tq = 0;
+          tq_phase ^= 1u;
+        }
+        if (t < 0) break;
         int b, ti, tj;
         decode_tile(p, t, b, ti, tj);
         const int m0 = ti * kBlockM;
@@ -315,8 +344,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       uint32_t phase = 0;
       int ab = 0;
       uint32_t aphase = 0;
+      int tq = 0;
+      uint32_t tq_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      while (ok) {
+        if (!mbar_wait(&tq_full_bar[tq], tq_phase)) {
+          report(p, kStatusTimeoutMma + 2u);
+          break;
+        }
+        const int t = tile_queue[tq];
+        mbar_arrive(&tq_empty_bar[tq]);
+        if (++tq == kTileQueue) {
+          tq = 0;
+          tq_phase ^= 1u;
+        }
+        if (t < 0) break;
         if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
           report(p, kStatusTimeoutMma);
           break;
@@ -357,7 +399,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int ab = 0;
     uint32_t aphase = 0;
-    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
+    int tq = 0;
+    uint32_t tq_phase = 0;
+    while (true) {
+      if (!mbar_wait(&tq_full_bar[tq], tq_phase)) {
+        report(p, kStatusTimeoutEpilogue + 1u);
+        break;
+      }
+      const int t = tile_queue[tq];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tq_empty_bar[tq]);
+      if (++tq == kTileQueue) {
+        tq = 0;
+        tq_phase ^= 1u;
+      }
+      if (t < 0) break;
       int b, ti, tj;
       decode_tile(p, t, b, ti, tj);
       const int m0 = ti * kBlockM;
@@ -399,6 +455,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    // Last CTA out re-arms the scheduler words for the next launch that is given this slot.
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
+      __threadfence();
+    }
   }
 }
 

@@ -203,6 +203,9 @@ int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t 
  *       out_stack + i * slot_stride - the stacked (n, rows, cols) input of a batched Newton-Schulz run.
  *       `p` may be NULL when l2_weight_decay == 0.  scratch: eo_muon_prepare_scratch_bytes(n, numel).
  *   eo_muon_apply_batch  : weight update of n tensors of any sizes; update[i] is bf16 or fp32 for all i.
+ *       max_blocks_per_tensor > 0 caps the grid (blocks of 256 threads per tensor) so that an update running
+ *       beside tensor-core kernels on another stream takes only a slice of the SMs and of HBM bandwidth;
+ *       0 sizes the grid for full bandwidth.
  *
  * Results are bit-identical to the single-tensor calls.
  */
@@ -211,7 +214,8 @@ int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const f
                           double momentum, int nesterov, float l2_weight_decay, float eps, void* out_stack,
                           int64_t slot_stride, double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
 int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int update_is_bf16, const int64_t* numel,
-                        const float* scale, float shrink, float extra_scale, float lr, void* stream);
+                        const float* scale, float shrink, float extra_scale, float lr, int max_blocks_per_tensor,
+                        void* stream);
 
 /*
  * The whole iteration loop of newton_schulz on the bf16 path in one call:
