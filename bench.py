@@ -227,7 +227,9 @@ def run_gpu_arm(args) -> None:
     side = torch.cuda.Stream(device=dev)
     gather_buf, peer = None, None
     slot = M * N_COLS
-    if world > 1:
+    if world > 1 and args.exchange == "nccl":
+        gather_buf = torch.empty(world, M, N_COLS, dtype=torch.bfloat16, device=dev)
+    elif world > 1:
         try:
             from emerging_optimizers_b200.distributed.peer_memory import PeerBuffer
 
@@ -501,6 +503,70 @@ def run_muon_step(args) -> None:
         dist.destroy_process_group()
 
 
+def run_tp_ns(args) -> None:
+    """Secondary workload (BASELINE config 4): tensor-parallel Newton-Schulz of one 8192 x 28672 matrix whose
+    columns are sharded over the N ranks; per iteration the partial Gram matrices are all-reduced (fused into the
+    SYRK epilogue, or NCCL with --exchange nccl).  Total work is fixed: "strong" scaling."""
+    import torch
+    import torch.distributed as dist
+
+    from emerging_optimizers_b200 import _native
+    from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+    from emerging_optimizers_b200.utils import fp32_matmul_precision
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.exchange == "nccl":
+        os.environ["EO_TP_GRAM"] = "nccl"
+    cols = N_COLS // world
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    x = torch.randn(M, cols, generator=g, device=dev)
+    group = dist.group.WORLD if world > 1 else None
+
+    def call():
+        with fp32_matmul_precision("medium"):
+            if world == 1:
+                return muon_utils.newton_schulz(x, NS_STEPS, COEFF, use_syrk=True)
+            return muon_utils.newton_schulz_tp(x, NS_STEPS, COEFF, group, partition_dim=1, tp_mode="distributed",
+                                               use_syrk=True)  # fmt: skip
+
+    for _ in range(max(args.warmup, 3)):
+        call()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    status = _native.read_device_status(dev)
+    if rank == 0:
+        dense, sym = flops(M, N_COLS, NS_STEPS)
+        ms = float(t[0])
+        print(json.dumps({
+            "metric": "tp_newton_schulz_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"tensor-parallel newton_schulz {M}x{N_COLS}, column shards of {cols}, "
+                       f"{NS_STEPS} '{COEFF}' steps, Gram exchange: {args.exchange if world > 1 else 'none'}"},
+            "tflops_dense_eq": dense / (ms / 1e3) / 1e12, "device_status": status,
+        }), flush=True)  # fmt: skip
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -512,7 +578,9 @@ def main() -> None:
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident timing only: no end-to-end loop, CPU baseline or clock sampling, and "
                     "--warmup taken as given (for profiler captures; not a benchmark number)")
-    ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step"],
+    ap.add_argument("--exchange", default="ce", choices=["ce", "nccl"],
+                    help="N > 1: exchange results by copy-engine pushes into symmetric memory (default) or by NCCL")
+    ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step", "tp_ns"],
                     help="newton_schulz (default, the headline metric) or muon_step (BASELINE config 3)")
     ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
     args = ap.parse_args()
@@ -523,6 +591,8 @@ def main() -> None:
         run_reference_arm(args)
     elif args.workload == "muon_step":
         run_muon_step(args)
+    elif args.workload == "tp_ns":
+        run_tp_ns(args)
     else:
         run_gpu_arm(args)
 

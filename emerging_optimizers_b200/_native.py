@@ -87,6 +87,12 @@ _PROTOTYPES: dict[str, tuple] = {
         [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int]
         + [c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
     ),
+    "eo_tp_gram_inbox_bytes": (c_size_t, [c_int, c_int]),
+    "eo_tp_gram_flag_count": (c_size_t, [c_int, c_int]),
+    "eo_tp_gram_allreduce": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_uint32, c_void_p],
+    ),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -523,3 +529,23 @@ def newton_schulz_bf16(
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_bf16")
     return out
+
+
+def tp_gram_allreduce(x: torch.Tensor, world: int, rank: int, inbox_ptrs, flag_ptrs, gram_ptrs, ld_gram: int, seq: int) -> None:
+    """Launch the fused tensor-parallel Gram exchange for this rank's bf16 shard ``x`` (see ``eo_tp_gram_allreduce``)."""
+    require_cuda(x, "x")
+    assert x.dtype == torch.bfloat16 and x.dim() == 2
+    mn, ld, _ = _mat_layout(x)
+
+    def arr(ptrs):
+        a = (c_void_p * world)()
+        for i, p in enumerate(ptrs):
+            a[i] = p
+        return a
+
+    with torch.cuda.device(x.device), _Timed("tp_gram", 2, x.device, timed=True):
+        rc = lib().eo_tp_gram_allreduce(
+            x.data_ptr(), mn, ld, x.size(0), x.size(1), world, rank, arr(inbox_ptrs), arr(flag_ptrs), arr(gram_ptrs),
+            ld_gram, seq, _stream(x),
+        )  # fmt: skip
+    _check(rc, "eo_tp_gram_allreduce")

@@ -14,6 +14,7 @@
 
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
+#include "tp_reduce.cuh"
 
 namespace {
 
@@ -116,10 +117,28 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
   return EO_OK;
 }
 
+// Tensor-parallel push target of a SYRK launch (see GemmParams::tp_*).
+struct TpPush {
+  int world, rank;
+  unsigned int seq;
+  void* const* inbox;         // [world] base of every rank's inbox
+  unsigned int* const* flags;  // [world] base of every rank's flag words
+};
+
+// Tile width of the tensor-parallel Gram exchange; the pushing and the reducing kernel must agree on it.
+inline int tp_tile_n(int N) { return N > 128 ? 256 : 128; }
+inline int tp_total_tiles(int N) {
+  const int bn = tp_tile_n(N), tm = (N + eo::kBlockM - 1) / eo::kBlockM, tn = (N + bn - 1) / bn;
+  int total = 0;
+  for (int j = 0; j < tn; ++j) total += tm - j * (bn / eo::kBlockM);
+  return total;
+}
+inline int tp_slots(int N, int world) { return (tp_total_tiles(N) + world - 1) / world; }
+
 int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t planeA, const void* B, int b_mn,
                 int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
                 int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
-                int round_bf16, int tri, int skip_upper, void* stream) {
+                int round_bf16, int tri, int skip_upper, void* stream, const TpPush* tp = nullptr) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(EO_ERR_BAD_ARG, "negative size");
@@ -128,7 +147,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   if (precision == 1 && (planeA % 8 != 0 || planeB % 8 != 0 || planeA <= 0 || planeB <= 0))
     return fail(EO_ERR_BAD_ARG, "plane strides must be positive multiples of 8 elements");
   if (beta != 0.0f && C == nullptr) return fail(EO_ERR_BAD_ARG, "beta != 0 needs C");
-  if (A == nullptr || B == nullptr || D == nullptr) {
+  if (A == nullptr || B == nullptr || (D == nullptr && tp == nullptr)) {
     if (batch == 0 || M == 0 || N == 0) return EO_OK;
     return fail(EO_ERR_BAD_ARG, "null operand");
   }
@@ -233,7 +252,19 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   int tn256 = 0, tn128 = 0;
   const long long t256 = static_cast<long long>(count_tiles(256, &tn256)) * batch;
   const long long t128 = static_cast<long long>(count_tiles(128, &tn128)) * batch;
-  const bool narrow = (N <= 128) || (t256 < dev->sm_count && t128 > t256);
+  bool narrow = (N <= 128) || (t256 < dev->sm_count && t128 > t256);
+  if (tp != nullptr) {
+    narrow = tp_tile_n(N) == 128;
+    p.tp_world = tp->world;
+    p.tp_rank = tp->rank;
+    p.tp_seq = tp->seq;
+    const int slots = tp_slots(N, tp->world);
+    const int64_t tile_elems = static_cast<int64_t>(eo::kBlockM) * tp_tile_n(N);
+    for (int r = 0; r < tp->world; ++r) {
+      p.tp_inbox[r] = static_cast<unsigned short*>(tp->inbox[r]) + static_cast<int64_t>(tp->rank) * slots * tile_elems;
+      p.tp_flags[r] = tp->flags[r] + static_cast<int64_t>(tp->rank) * slots;
+    }
+  }
   p.bn = narrow ? 128 : 256;
   p.tiles_n = narrow ? tn128 : tn256;
   const long long total = narrow ? t128 : t256;
@@ -582,6 +613,71 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
     cur_ld = dst_ld;
     cur_stride = dst_stride;
   }
+  return EO_OK;
+}
+
+size_t eo_tp_gram_inbox_bytes(int N, int world) {
+  if (N <= 0 || world <= 0) return 0;
+  return static_cast<size_t>(world) * tp_slots(N, world) * eo::kBlockM * tp_tile_n(N) * 2;
+}
+
+size_t eo_tp_gram_flag_count(int N, int world) {
+  if (N <= 0 || world <= 0) return 0;
+  return static_cast<size_t>(world) * tp_slots(N, world);
+}
+
+int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, int world, int rank,
+                         void* const* inbox_ptrs, void* const* flag_ptrs, void* const* gram_ptrs, int64_t ld_gram,
+                         uint32_t seq, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (world < 2 || world > 8 || rank < 0 || rank >= world) return fail(EO_ERR_BAD_ARG, "world must be 2..8");
+  if (N <= 0 || K <= 0 || N % 8 != 0) return fail(EO_ERR_BAD_ARG, "N must be a positive multiple of 8, K positive");
+  if (X == nullptr || inbox_ptrs == nullptr || flag_ptrs == nullptr || gram_ptrs == nullptr)
+    return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (ld_gram < N || ld_gram % 8 != 0) return fail(EO_ERR_BAD_ARG, "ld_gram must be a multiple of 8 and >= N");
+  for (int r = 0; r < world; ++r) {
+    if (inbox_ptrs[r] == nullptr || flag_ptrs[r] == nullptr || gram_ptrs[r] == nullptr)
+      return fail(EO_ERR_BAD_ARG, "null peer pointer for rank %d", r);
+    if ((reinterpret_cast<uintptr_t>(inbox_ptrs[r]) | reinterpret_cast<uintptr_t>(gram_ptrs[r])) & 15)
+      return fail(EO_ERR_BAD_ARG, "peer buffers must be 16-byte aligned");
+  }
+  unsigned int* flags[8];
+  for (int r = 0; r < world; ++r) flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
+  TpPush tp{world, rank, seq, inbox_ptrs, flags};
+  // 1. partial Gram tiles pushed to their owners from the SYRK epilogue
+  int rc = launch_gemm(X, x_trans, ldx, 0, 0, X, x_trans, ldx, 0, 0, nullptr, 0, 0, nullptr, 0, 0, 1, N, N, K, 1.0f,
+                       0.0f, 1.0f, 0, 0, 0, /*tri=*/1, 0, stream, &tp);
+  if (rc) return rc;
+  // 2. owners reduce their tiles and store them (and their mirror images) into every rank's Gram matrix
+  eo::TpReduceParams q;
+  memset(&q, 0, sizeof(q));
+  q.N = N;
+  q.bn = tp_tile_n(N);
+  q.world = world;
+  q.rank = rank;
+  q.seq = seq;
+  q.tiles_m = (N + eo::kBlockM - 1) / eo::kBlockM;
+  q.tiles_n = (N + q.bn - 1) / q.bn;
+  q.total_tiles = tp_total_tiles(N);
+  q.slots = tp_slots(N, world);
+  q.inbox = static_cast<const unsigned short*>(inbox_ptrs[rank]);
+  q.flags = flags[rank];
+  for (int r = 0; r < world; ++r) q.gram[r] = static_cast<unsigned short*>(gram_ptrs[r]);
+  q.ld = ld_gram;
+  q.status = dev->status_ptr;
+  const int smem = eo::kBlockM * (q.bn + 8) * 2;
+  static bool attr_set[kMaxDevices] = {};
+  int devid = 0;
+  EO_CUDA(cudaGetDevice(&devid));
+  if (!attr_set[devid]) {
+    EO_CUDA(cudaFuncSetAttribute(eo::tp_gram_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kBlockM * (256 + 8) * 2));
+    attr_set[devid] = true;
+  }
+  const int grid = q.slots < 2 * dev->sm_count ? q.slots : 2 * dev->sm_count;
+  eo::tp_gram_reduce_kernel<<<grid, eo::kTpReduceThreads, smem, static_cast<cudaStream_t>(stream)>>>(q);
+  EO_CUDA(cudaGetLastError());
   return EO_OK;
 }
 

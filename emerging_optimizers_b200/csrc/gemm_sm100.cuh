@@ -68,6 +68,13 @@ struct GemmParams {
   // that starts late or shares its SM with another kernel simply takes fewer tiles.  `sched[1]` counts CTAs that
   // have finished; the last one zeroes both words for the next launch that uses this slot.
   unsigned int* sched;
+  // Tensor-parallel Gram mode (tp_world > 1, with tri): instead of storing D, the epilogue pushes the bf16 partial
+  // tile t into the inbox of its owner rank (t % tp_world) - plain stores to local or peer memory - and then
+  // publishes a sequence number in the owner's flag word for (this rank, t / tp_world).
+  int tp_world, tp_rank;
+  unsigned int tp_seq;
+  unsigned short* tp_inbox[8];  // per owner: base of the region this rank writes, [slot][128][bn] bf16
+  unsigned int* tp_flags[8];    // per owner: flag words of this rank, [slot]
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
@@ -220,6 +227,25 @@ struct GemmMaps {
   CUtensorMap b[kMaxPlanes];
 };
 
+// Tensor-parallel push of one 32-column chunk of a partial tile: alpha * acc rounded to bf16, 64 contiguous
+// bytes per thread at [row_local][col_local .. +32) of the tile image in the owner's inbox.
+__device__ __forceinline__ void push_chunk(const GemmParams& p, const uint32_t (&acc)[32], unsigned short* tile,
+                                           int row_local, int col_local) {
+  unsigned short* dst = tile + static_cast<long long>(row_local) * p.bn + col_local;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    unsigned int w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const unsigned int lo = __bfloat16_as_ushort(__float2bfloat16_rn(p.alpha * __uint_as_float(acc[8 * q + 2 * e])));
+      const unsigned int hi =
+          __bfloat16_as_ushort(__float2bfloat16_rn(p.alpha * __uint_as_float(acc[8 * q + 2 * e + 1])));
+      w[e] = lo | (hi << 16);
+    }
+    reinterpret_cast<uint4*>(dst)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1)
     eo_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -234,6 +260,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tq_empty_bar = tq_full_bar + kTileQueue;  // [kTileQueue]
   int* tile_queue = reinterpret_cast<int*>(tq_empty_bar + kTileQueue);  // [kTileQueue]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_queue + kTileQueue);
+  unsigned int* push_done = tmem_slot + 1;  // [2] epilogue warps that finished pushing the tile in accumulator ab
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -251,6 +278,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       mbar_init(&tq_full_bar[s], 1);
       mbar_init(&tq_empty_bar[s], 5);  // MMA thread + four epilogue warps
     }
+    push_done[0] = 0u;
+    push_done[1] = 0u;
     mbar_init_fence();
     for (int t = 0; t < p.nterms; ++t) {
       tma_prefetch_desc(&maps.a[p.term_a[t]]);
@@ -428,17 +457,43 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const long long batch_c = static_cast<long long>(b) * p.strideC;
       const long long batch_d = static_cast<long long>(b) * p.strideD;
       const int nchunks = p.bn / 32;
-      for (int c = 0; c < nchunks; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;
-        if (p.tri && col0 > warp_last_row) break;  // whole chunk lies above the diagonal for this warp
-        uint32_t acc[32];
+      if (p.tp_world > 1) {
+        // Push the whole partial tile to its owner, then let the last of the four warps publish the flag.
+        const int owner = t % p.tp_world;
+        const int slot = t / p.tp_world;
+        unsigned short* tile = p.tp_inbox[owner] + static_cast<long long>(slot) * kBlockM * p.bn;
+        for (int c = 0; c < nchunks; ++c) {
+          uint32_t acc[32];
+          __syncwarp();
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                            static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
+                        acc);
+          tmem_ld_wait();
+          push_chunk(p, acc, tile, quarter * 32 + lane, c * 32);
+        }
+        __threadfence_system();
         __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                          static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
-                      acc);
-        tmem_ld_wait();
-        epilogue_chunk(p, acc, batch_c, batch_d, row, col0);
+        if (lane == 0) {
+          if (atomicAdd(&push_done[ab], 1u) == 3u) {
+            push_done[ab] = 0u;
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[owner] + slot), "r"(p.tp_seq)
+                         : "memory");
+          }
+        }
+      } else {
+        for (int c = 0; c < nchunks; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          if (p.tri && col0 > warp_last_row) break;  // whole chunk lies above the diagonal for this warp
+          uint32_t acc[32];
+          __syncwarp();
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                            static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
+                        acc);
+          tmem_ld_wait();
+          epilogue_chunk(p, acc, batch_c, batch_d, row, col0);
+        }
       }
       tc_fence_before();
       __syncwarp();

@@ -232,6 +232,16 @@ def _ns_step(
     _native.require_cuda(X, "X")
     X = _prepare(X)
     x_op = _native.Split3(X) if _is_split(X) else X
+    if tp_group is not None and use_syrk and X.is_cuda:
+        from emerging_optimizers_b200.distributed import tensor_parallel
+
+        if tensor_parallel.fused_gram_available(X, tp_group):
+            # Gram all-reduce fused into the SYRK epilogue (peer stores over NVLink), see tensor_parallel.py.
+            A = tensor_parallel.fused_gram(X, tp_group)
+            if c != 0.0:
+                S = _gram_poly(A, b, c, use_syrk)
+                return _apply(S, X, 1.0, a, out_fp32, x_op)
+            return _apply(A, X, b, a, out_fp32, x_op)
     A = _gram(X, use_syrk, x_op)
     if tp_group is not None:
         if not A.is_contiguous():

@@ -1,0 +1,93 @@
+"""Tensor-parallel Newton-Schulz on two GPUs: the Gram all-reduce fused into the SYRK epilogue against exact integer
+sums, against the NCCL all-reduce path and against single-device Newton-Schulz on the gathered matrix."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from emerging_optimizers_b200 import _native as nat
+from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+from emerging_optimizers_b200.utils import fp32_matmul_precision
+
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _randn(*shape, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32)
+
+
+def _rel(a, b):
+    return float((a.double() - b.double()).norm() / b.double().norm())
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    group = dist.group.WORLD
+    from emerging_optimizers_b200.distributed import tensor_parallel as tp
+
+    res = {}
+    # 1. the exchange alone, integer-valued shards: every partial and the sum are exact in bf16
+    for m, k in ((128, 64), (200, 64), (1000, 64), (512, 128)):
+        g = torch.Generator(device="cpu").manual_seed(100 + m)
+        full = torch.randint(-1, 2, (m, world * k), generator=g).to(torch.bfloat16)
+        for trans in (False, True):
+            shard = full[:, rank * k : (rank + 1) * k].contiguous().to(dev)
+            if trans:
+                shard = shard.T.contiguous().T
+            for rep in range(2):  # second call reuses inbox, flags and Gram buffer with the next sequence number
+                a = tp.fused_gram(shard, group).clone()
+            want = (full.float() @ full.float().T).to(dev)
+            res[f"gram.{m}.{int(trans)}"] = bool(torch.equal(a.float(), want)) and bool(torch.equal(a, a.T))
+    # 2. full tensor-parallel Newton-Schulz, both partition dims, fused exchange vs NCCL vs single device
+    for shape, pdim in (((512, 2048), 1), ((2048, 512), 0), ((256, 1024), 1)):
+        x = _randn(*shape, seed=7)
+        shard = x.chunk(world, dim=pdim)[rank].contiguous().to(dev)
+        with fp32_matmul_precision("medium"):
+            y_fused = muon_utils.newton_schulz_tp(shard, 5, "quintic", group, partition_dim=pdim,
+                                                  tp_mode="distributed", use_syrk=True)  # fmt: skip
+            os.environ["EO_TP_GRAM"] = "nccl"
+            y_nccl = muon_utils.newton_schulz_tp(shard, 5, "quintic", group, partition_dim=pdim,
+                                                 tp_mode="distributed", use_syrk=True)  # fmt: skip
+            os.environ["EO_TP_GRAM"] = "fused"
+            y_full = muon_utils.newton_schulz(x.to(dev), 5, "quintic", use_syrk=True)
+        ref = y_full.chunk(world, dim=pdim)[rank]
+        res[f"ns.{shape}.{pdim}"] = (_rel(y_fused, ref), _rel(y_nccl, ref), tuple(y_fused.shape) == tuple(shard.shape))
+    torch.cuda.synchronize()
+    res["status"] = nat.read_device_status(dev)
+    out[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_gram_exchange_and_tp_newton_schulz_two_gpus():
+    world = 2
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        results = dict(out)
+    for rank in range(world):
+        res = results[rank]
+        assert res["status"] == 0
+        for key, val in res.items():
+            if key.startswith("gram."):
+                assert val, (rank, key)
+            elif key.startswith("ns."):
+                err_fused, err_nccl, shape_ok = val
+                assert shape_ok
+                # bf16 path tolerance against single-device Newton-Schulz on the gathered matrix
+                assert err_fused <= 2e-2 and err_nccl <= 2e-2, (rank, key, val)
