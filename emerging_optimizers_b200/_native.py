@@ -133,7 +133,8 @@ class NativeLibraryError(RuntimeError):
 
 
 def library_path() -> str:
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), _LIB_NAME)
+    """Path of the shared library; ``EO_B200_LIB`` overrides the in-tree default (e.g. to compare two builds)."""
+    return os.environ.get("EO_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), _LIB_NAME)
 
 
 def exported_symbols() -> list[str]:

@@ -197,6 +197,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     }
   }
   p.tri = tri;
+  p.same_ab = (tri && precision == 0 && A == B && a_mn == b_mn && lda == ldb && strideA == strideB && planeA == planeB) ? 1 : 0;
   p.skip_upper = skip_upper;
   p.c_fp32 = precision;
   p.d_fp32 = d_fp32;
@@ -224,12 +225,6 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   p.lbo_b = b_mn ? mn_lbo : 0u;
   p.sbo_a = 1024u;
   p.sbo_b = 1024u;
-#ifdef EO_BRINGUP
-  if (const char* e = getenv("EO_DBG_MN_LBO")) { if (a_mn) p.lbo_a = atoi(e); if (b_mn) p.lbo_b = atoi(e); }
-  if (const char* e = getenv("EO_DBG_MN_SBO")) { if (a_mn) p.sbo_a = atoi(e); if (b_mn) p.sbo_b = atoi(e); }
-  if (const char* e = getenv("EO_DBG_MN_ADV")) { if (a_mn) p.adv_a = atoi(e); if (b_mn) p.adv_b = atoi(e); }
-  if (const char* e = getenv("EO_DBG_K_LBO")) { if (!a_mn) p.lbo_a = atoi(e); if (!b_mn) p.lbo_b = atoi(e); }
-#endif
 
   const int c_eb = p.c_fp32 ? 4 : 2;
   const int d_eb = p.d_fp32 ? 4 : 2;
@@ -301,7 +296,9 @@ int eo_read_device_status(uint32_t* host_code, void* stream) {
   EO_CUDA(cudaMemcpyAsync(&code, dev->status_ptr, sizeof(code), cudaMemcpyDeviceToHost, s));
   EO_CUDA(cudaStreamSynchronize(s));
   if (code != 0) {
+    // A kernel that gave up may have left its tile-scheduler words non-zero: re-arm all of them.
     EO_CUDA(cudaMemsetAsync(dev->status_ptr, 0, sizeof(code), s));
+    EO_CUDA(cudaMemsetAsync(dev->sched_ptr, 0, 2 * kSchedSlots * sizeof(unsigned int), s));
     EO_CUDA(cudaStreamSynchronize(s));
   }
   *host_code = code;

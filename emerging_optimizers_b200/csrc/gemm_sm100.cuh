@@ -7,10 +7,11 @@
 // M == N): only tiles touching the lower triangle are computed, the lower part is stored and,
 // unless `skip_upper`, mirrored into the upper part, so that every output element is written once.
 //
-// One CTA per SM, 192 threads:
+// One CTA per SM, 320 threads:
 //   warp 0      TMA producer   (global -> 128B-swizzled shared-memory ring, kStages deep)
 //   warp 1      MMA issuer     (one elected thread issues tcgen05.mma, accumulators in TMEM)
-//   warps 2..5  epilogue       (tcgen05.ld -> alpha/beta -> round -> global stores)
+//   warps 2..9  epilogue       (tcgen05.ld -> alpha/beta -> round -> global stores; two warps per TMEM
+//                               lane quarter, so that twice as many C loads and D stores are in flight)
 // TMEM holds two 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the main loop of
 // tile t+1.  Every wait is bounded; a wait that runs out records a code in the status word and the
 // role leaves its loop.
@@ -31,7 +32,11 @@ constexpr int kStages = 4;
 constexpr int kStageABytes = kBlockM * kRowBytes;     // 16 KiB
 constexpr int kStageBBytes = kMaxBlockN * kRowBytes;  // 32 KiB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;
-constexpr int kGemmThreads = 192;
+#ifndef EO_EPILOGUE_WARPS
+#define EO_EPILOGUE_WARPS 8
+#endif
+constexpr int kEpilogueWarps = EO_EPILOGUE_WARPS;  // 4 or 8: one or two per TMEM lane quarter, alternating 32-column chunks
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 16;  // row-block group height of the general tile order
 
@@ -48,6 +53,8 @@ struct GemmParams {
   int term_a[6];   // plane of A used by term t
   int term_b[6];   // plane of B used by term t
   int tri;         // symmetric update: lower-triangle tiles only
+  int same_ab;     // A and B are the same matrix (SYRK): a tile whose rows lie inside its column range reads
+                   // its A operand out of the B tile instead of loading it a second time
   int skip_upper;  // with tri: do not mirror into the upper triangle
   int c_fp32;      // element type of C: fp32 (1) or bf16 (0)
   int d_fp32;      // element type of D
@@ -272,11 +279,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
-      mbar_init(&acc_empty_bar[s], 4);
+      mbar_init(&acc_empty_bar[s], kEpilogueWarps);
     }
     for (int s = 0; s < kTileQueue; ++s) {
       mbar_init(&tq_full_bar[s], 1);
-      mbar_init(&tq_empty_bar[s], 5);  // MMA thread + four epilogue warps
+      mbar_init(&tq_empty_bar[s], 1 + kEpilogueWarps);  // MMA thread + epilogue warps
     }
     push_done[0] = 0u;
     push_done[1] = 0u;
@@ -327,6 +334,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         decode_tile(p, t, b, ti, tj);
         const int m0 = ti * kBlockM;
         const int n0 = tj * p.bn;
+        // SYRK tile on the diagonal: its 128 rows are among the rows of the B tile, which then serves both operands.
+        const bool a_in_b = p.same_ab && m0 >= n0 && m0 + kBlockM <= n0 + p.bn;
+        const uint32_t tx = a_in_b ? static_cast<uint32_t>(p.bn * kRowBytes) : stage_tx;
         int term = 0, kb = 0;
         for (int it = 0; it < num_it; ++it) {
           const CUtensorMap* tmA = &maps.a[p.term_a[term]];
@@ -338,9 +348,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kStageABytes;
-          mbar_expect_tx(&full_bar[stage], stage_tx);
+          mbar_expect_tx(&full_bar[stage], tx);
           const int k0 = kb * bk;
-          if (!p.a_mn) {
+          if (a_in_b) {
+            // nothing to load for A
+          } else if (!p.a_mn) {
             tma_load_3d(sa, tmA, &full_bar[stage], k0, m0, b);  // box {bk, 128, 1}
           } else {
             // box {bk (M), bk (K), 1}: one 128-byte-wide M atom per copy
@@ -394,6 +406,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
+        // Offset of the A operand inside the stage: its own slot, or its rows inside the B tile (see the producer).
+        uint32_t a_off = 0;
+        if (p.same_ab) {
+          int b, ti, tj;
+          decode_tile(p, t, b, ti, tj);
+          const int m0 = ti * kBlockM, n0 = tj * p.bn;
+          if (m0 >= n0 && m0 + kBlockM <= n0 + p.bn) a_off = static_cast<uint32_t>(kStageABytes + (m0 - n0) * kRowBytes);
+        }
         for (int it = 0; it < num_it; ++it) {
           if (!mbar_wait(&full_bar[stage], phase)) {
             report(p, kStatusTimeoutMma + 1u);
@@ -405,7 +425,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sb = sa + kStageABytes;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_smem_desc(sa + k * p.adv_a, p.lbo_a, p.sbo_a);
+            const uint64_t da = make_smem_desc(sa + a_off + k * p.adv_a, p.lbo_a, p.sbo_a);
             const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
             umma_f16(tmem_d, da, db, idesc, (it | k) != 0 ? 1u : 0u);
           }
@@ -425,7 +445,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const int chunk0 = (warp - 2) >> 2;    // this warp takes chunks chunk0, chunk0 + 2, ...
+    constexpr int kChunkStep = kEpilogueWarps / 4;
     int ab = 0;
     uint32_t aphase = 0;
     int tq = 0;
@@ -462,7 +484,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int owner = t % p.tp_world;
         const int slot = t / p.tp_world;
         unsigned short* tile = p.tp_inbox[owner] + static_cast<long long>(slot) * kBlockM * p.bn;
-        for (int c = 0; c < nchunks; ++c) {
+        for (int c = chunk0; c < nchunks; c += kChunkStep) {
           uint32_t acc[32];
           __syncwarp();
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -474,7 +496,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
-          if (atomicAdd(&push_done[ab], 1u) == 3u) {
+          if (atomicAdd(&push_done[ab], 1u) == static_cast<unsigned int>(kEpilogueWarps - 1)) {
             push_done[ab] = 0u;
             __threadfence_system();
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[owner] + slot), "r"(p.tp_seq)
@@ -482,7 +504,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           }
         }
       } else {
-        for (int c = 0; c < nchunks; ++c) {
+        for (int c = chunk0; c < nchunks; c += kChunkStep) {
           const int col0 = n0 + c * 32;
           if (col0 >= p.N) break;
           if (p.tri && col0 > warp_last_row) break;  // whole chunk lies above the diagonal for this warp
