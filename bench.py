@@ -521,8 +521,7 @@ def run_tp_ns(args) -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    if args.exchange == "nccl":
-        os.environ["EO_TP_GRAM"] = "nccl"
+    os.environ["EO_TP_GRAM"] = "nccl" if args.exchange == "nccl" else "fused"
     cols = N_COLS // world
     g = torch.Generator(device=dev).manual_seed(3 + rank)
     x = torch.randn(M, cols, generator=g, device=dev)

@@ -55,14 +55,27 @@ class GramExchange:
         return self.gram.local.view(self.m, self.ld)[:, : self.m]
 
 
+# Largest group for which the fused exchange is chosen by default.  Measured on 8192 x 28672 (five steps, B200,
+# NVSwitch): fused 16.4 / 10.1 / 8.2 ms on 2 / 4 / 8 ranks against 16.3 / 10.3 / 7.4 ms with NCCL's all-reduce; on 8
+# ranks the owners' point-to-point broadcast of the reduced tiles loses to the in-switch reduction NCCL uses.
+FUSED_MAX_WORLD = 4
+
+
 def fused_gram_available(x: torch.Tensor, group: "dist.ProcessGroup | None") -> bool:
-    """The fused exchange takes 2-D bf16 CUDA shards with TMA-addressable sizes on 2..8 ranks."""
+    """Whether the fused exchange is used for this shard: 2-D bf16 CUDA, TMA-addressable sizes, 2..8 ranks.
+
+    ``EO_TP_GRAM=fused`` / ``EO_TP_GRAM=nccl`` force one or the other; by default (``auto``) groups of up to
+    ``FUSED_MAX_WORLD`` ranks take the fused exchange and larger ones NCCL.
+    """
     if group is None or not x.is_cuda or x.dim() != 2 or x.dtype != torch.bfloat16:
         return False
-    if os.environ.get("EO_TP_GRAM", "fused") != "fused":
+    mode = os.environ.get("EO_TP_GRAM", "auto")
+    if mode == "nccl":
         return False
     world = dist.get_world_size(group)
-    return 2 <= world <= 8 and x.size(0) % 8 == 0 and x.size(1) % 8 == 0
+    if not (2 <= world <= 8 and x.size(0) % 8 == 0 and x.size(1) % 8 == 0):
+        return False
+    return mode == "fused" or world <= FUSED_MAX_WORLD
 
 
 def fused_gram(x: torch.Tensor, group: "dist.ProcessGroup") -> torch.Tensor:

@@ -63,7 +63,7 @@ def _worker(rank, world, port, out):
             os.environ["EO_TP_GRAM"] = "nccl"
             y_nccl = muon_utils.newton_schulz_tp(shard, 5, "quintic", group, partition_dim=pdim,
                                                  tp_mode="distributed", use_syrk=True)  # fmt: skip
-            os.environ["EO_TP_GRAM"] = "fused"
+            os.environ["EO_TP_GRAM"] = "auto"
             y_full = muon_utils.newton_schulz(x.to(dev), 5, "quintic", use_syrk=True)
         ref = y_full.chunk(world, dim=pdim)[rank]
         res[f"ns.{shape}.{pdim}"] = (_rel(y_fused, ref), _rel(y_nccl, ref), tuple(y_fused.shape) == tuple(shard.shape))
