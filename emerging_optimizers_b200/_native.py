@@ -506,6 +506,10 @@ def muon_apply_batch(
     _check(rc, "eo_muon_apply_batch")
 
 
+# Set to False to keep small matrices (rows <= 128) on the general kernels (comparison runs).
+FUSED_SMALL_MATRICES = True
+
+
 def newton_schulz_bf16(
     x: torch.Tensor, schedule, use_syrk: bool, out_dtype: torch.dtype = torch.bfloat16
 ) -> torch.Tensor:
@@ -525,7 +529,8 @@ def newton_schulz_bf16(
     with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
         rc = lib().eo_newton_schulz_bf16(
             x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
-            1 if use_syrk else 0, out.data_ptr(), 1 if out_dtype == torch.float32 else 0, cols, rows * cols,
+            (1 if use_syrk else 0) | (0 if FUSED_SMALL_MATRICES else 2),
+            out.data_ptr(), 1 if out_dtype == torch.float32 else 0, cols, rows * cols,
             ws.data_ptr(), nbytes, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_bf16")

@@ -14,6 +14,7 @@
 
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
+#include "ns_small_sm100.cuh"
 #include "tp_reduce.cuh"
 
 namespace {
@@ -80,6 +81,8 @@ int device_setup(DeviceInfo** out) {
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.sched_ptr), g_sched_words));
     EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_ns_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kSmallSmemBytes));
     if (g_encode == nullptr) {
       void* fn = nullptr;
       cudaDriverEntryPointQueryResult qres;
@@ -541,9 +544,49 @@ size_t eo_newton_schulz_workspace_bytes(int batch, int rows, int cols) {
   return static_cast<size_t>(2 * L.a_elems + L.t_elems) * 2;
 }
 
+namespace {
+// All iterations of a batch of small wide matrices (rows <= 128 <= ... cols) in one persistent kernel.
+int launch_ns_small(DeviceInfo* dev, void* X, int batch, int rows, int cols, int64_t ld, int64_t stride,
+                    const float* host_abc, int steps, void* T, int64_t ldt, int64_t t_stride, void* out, int out_fp32,
+                    int64_t ldo, int64_t strideo, void* stream) {
+  eo::SmallMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  if (int rc = make_map(&maps.x[0], X, 2, cols, rows, batch, ld, stride, 64, 128)) return rc;
+  if (int rc = make_map(&maps.x[1], T, 2, cols, rows, batch, ldt, t_stride, 64, 128)) return rc;
+  eo::SmallParams p;
+  memset(&p, 0, sizeof(p));
+  p.batch = batch;
+  p.m = rows;
+  p.n = cols;
+  p.steps = steps;
+  for (int i = 0; i < 3 * steps; ++i) p.abc[i] = host_abc[i];
+  p.buf[0] = static_cast<unsigned short*>(X);
+  p.buf[1] = static_cast<unsigned short*>(T);
+  p.ld[0] = ld;
+  p.stride[0] = stride;
+  p.ld[1] = ldt;
+  p.stride[1] = t_stride;
+  p.out = out;
+  p.ldo = ldo;
+  p.strideo = strideo;
+  p.out_fp32 = out_fp32;
+  p.status = dev->status_ptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    p.sched = dev->sched_ptr + 2 * (dev->sched_next % kSchedSlots);
+    dev->sched_next++;
+  }
+  const int grid = batch < dev->sm_count ? batch : dev->sm_count;
+  eo::eo_ns_small_kernel<<<grid, eo::kSmallThreads, eo::kSmallSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+}  // namespace
+
 int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
-                          int steps, int use_syrk, void* out, int out_fp32, int64_t ldo, int64_t strideo,
+                          int steps, int flags, void* out, int out_fp32, int64_t ldo, int64_t strideo,
                           void* workspace, size_t workspace_bytes, void* stream) {
+  const int use_syrk = flags & 1;
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || rows < 0 || cols < 0 || steps < 1) return fail(EO_ERR_BAD_ARG, "bad size or steps < 1");
@@ -561,6 +604,11 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
   void* T = ws + 2 * L.a_elems * 2;
   const int64_t a_stride = static_cast<int64_t>(L.m) * L.ldm;
   const int syrk = use_syrk && (rows % 8 == 0) && (cols % 8 == 0);
+
+  // Matrices whose Gram matrix is a single tile take the fused kernel: A, A^2 and S stay in shared memory.
+  if (!(flags & 2) && rows <= 128 && rows <= cols && cols >= 256 && steps <= eo::kSmallMaxSteps)
+    return launch_ns_small(dev, X, batch, rows, cols, ld, stride, host_abc, steps, T, L.ldt, L.t_stride, out, out_fp32,
+                           ldo, strideo, stream);
 
   // Iterate buffers: step i reads `cur` and writes `nxt`; the last step writes `out`.
   void* cur = X;

@@ -1,0 +1,510 @@
+// Whole Newton-Schulz loop for small matrices (m <= 128 rows, wide: m <= n) in ONE persistent kernel.
+//
+// Per-head / split-QKV blocks are 128 x n: their Gram matrix is a single 128 x 128 tile, so A = X X^T, A^2 and
+// S = b A + c A^2 never have to leave the SM.  A CTA takes one matrix at a time (dynamic counter) and runs all
+// iterations on it:
+//
+//   Gram   : X streamed through a shared-memory ring in 128 x 64 boxes (K-major), accumulated in TMEM;
+//            the epilogue rounds A to bf16 and writes it into shared memory in the 128B-swizzled operand layout
+//   A^2    : tcgen05.mma on the shared-memory copy of A (skipped when c == 0); epilogue writes S likewise
+//   S X    : X streamed again, 128 x 256 output tiles (the same boxes now act as MN-major B operands, four
+//            N = 64 MMAs per k-step), epilogue adds a X and writes the next iterate to global memory
+//
+// so per iteration a matrix is read twice and written once, with no launch boundary, no global A / S traffic and
+// no per-launch tail.  Roles as in the general kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue.
+// Every wait is bounded; a wait that runs out records a code in the status word and the CTA drains.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "sm100_ptx.cuh"
+
+namespace eo {
+
+constexpr int kSmallUnitBytes = 128 * 128;  // one TMA box: 128 rows x 64 bf16
+constexpr int kSmallUnits = 10;             // ring depth
+constexpr int kSmallABytes = 2 * kSmallUnitBytes;  // 128 x 128 bf16 operand (two 64-column atoms)
+constexpr int kSmallThreads = 64 + 32 * 8;
+constexpr int kSmallSmemBytes = kSmallUnits * kSmallUnitBytes + 2 * kSmallABytes + 1024 + 1024;
+constexpr int kSmallMaxSteps = 16;
+constexpr uint32_t kStatusSmall = 0x50u;
+
+struct SmallParams {
+  int batch, m, n;
+  int steps;
+  float abc[3 * kSmallMaxSteps];
+  unsigned short* buf[2];  // ping-pong iterates: buf[0] holds the input; iteration i reads buf[i & 1]
+  long long ld[2], stride[2];  // their layouts (elements)
+  void* out;               // result of the last iteration
+  long long ldo, strideo;
+  int out_fp32;
+  unsigned int* sched;   // {next matrix, finished CTAs}
+  unsigned int* status;
+};
+
+struct SmallMaps {
+  CUtensorMap x[2];  // over buf[0] and buf[1]: dims {n, m, batch}, box {64, 128, 1}, 128B swizzle
+};
+
+__device__ __forceinline__ uint32_t swz_offset(int row, int col) {
+  // byte offset of element (row, col) of a 128 x 128 bf16 operand stored as two 64-column, 128B-swizzled atoms
+  const int atom = col >> 6, unit = (col & 63) >> 3;
+  return static_cast<uint32_t>(atom * kSmallUnitBytes + row * 128 + (((unit ^ (row & 7)) << 4)) + ((col & 7) << 1));
+}
+
+__global__ void __launch_bounds__(kSmallThreads, 1)
+    eo_ns_small_kernel(const __grid_constant__ SmallMaps maps, const SmallParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;
+  uint8_t* a_buf = smem + kSmallUnits * kSmallUnitBytes;
+  uint8_t* s_buf = a_buf + kSmallABytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_buf + kSmallABytes);
+  uint64_t* full_bar = bars;                       // [kSmallUnits]
+  uint64_t* empty_bar = full_bar + kSmallUnits;    // [kSmallUnits]
+  uint64_t* acc_full_bar = empty_bar + kSmallUnits;  // [2]
+  uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2]
+  uint64_t* a_ready_bar = acc_empty_bar + 2;         // A written to shared memory
+  uint64_t* s_ready_bar = a_ready_bar + 1;           // S written to shared memory
+  uint64_t* x_ready_bar = s_ready_bar + 1;           // every tile of the next iterate written to global memory
+  uint64_t* mq_full_bar = x_ready_bar + 1;           // [2] matrix-index queue
+  uint64_t* mq_empty_bar = mq_full_bar + 2;          // [2]
+  int* mat_queue = reinterpret_cast<int*>(mq_empty_bar + 2);  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mat_queue + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nk = (p.n + 63) / 64;      // Gram k-blocks
+  const int nt = (p.n + 255) / 256;    // output tiles of the S X product
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSmallUnits; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], 8);
+      mbar_init(&mq_full_bar[s], 1);
+      mbar_init(&mq_empty_bar[s], 9);
+    }
+    mbar_init(a_ready_bar, 8);
+    mbar_init(s_ready_bar, 8);
+    mbar_init(x_ready_bar, 8u * static_cast<uint32_t>(nt));
+    mbar_init_fence();
+    tma_prefetch_desc(&maps.x[0]);
+    tma_prefetch_desc(&maps.x[1]);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto fail = [&](uint32_t code) {
+    if (p.status != nullptr) atomicCAS(p.status, 0u, kStatusSmall + code);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (elect_one()) {
+      int unit = 0;
+      uint32_t uphase = 0;
+      int mq = 0;
+      uint32_t mq_phase = 0, x_phase = 0;
+      bool ok = true;
+      auto load_unit = [&](const CUtensorMap* map, int col, int b) -> bool {
+        if (!mbar_wait(&empty_bar[unit], uphase ^ 1u)) {
+          fail(1);
+          return false;
+        }
+        mbar_expect_tx(&full_bar[unit], kSmallUnitBytes);
+        tma_load_3d(ring + unit * kSmallUnitBytes, map, &full_bar[unit], col, 0, b);
+        if (++unit == kSmallUnits) {
+          unit = 0;
+          uphase ^= 1u;
+        }
+        return true;
+      };
+      while (ok) {
+        int b = static_cast<int>(atomicAdd(p.sched, 1u));
+        if (b >= p.batch) b = -1;
+        if (!mbar_wait(&mq_empty_bar[mq], mq_phase ^ 1u)) {
+          fail(2);
+          break;
+        }
+        mat_queue[mq] = b;
+        mbar_arrive(&mq_full_bar[mq]);
+        if (++mq == 2) {
+          mq = 0;
+          mq_phase ^= 1u;
+        }
+        if (b < 0) break;
+        for (int it = 0; it < p.steps && ok; ++it) {
+          const CUtensorMap* map = &maps.x[it & 1];
+          if (it > 0) {
+            // the previous iteration's output must be complete in global memory before it is read back
+            if (!mbar_wait(x_ready_bar, x_phase)) {
+              fail(3);
+              ok = false;
+              break;
+            }
+            x_phase ^= 1u;
+          }
+          for (int kb = 0; kb < nk && ok; ++kb) ok = load_unit(map, kb * 64, b);
+          for (int t = 0; t < nt && ok; ++t)
+            for (int q = 0; q < 4 && ok; ++q) ok = load_unit(map, t * 256 + q * 64, b);
+        }
+        // The output tiles of the last iteration also arrive on x_ready: consume that phase.
+        if (ok && p.steps > 0) {
+          if (!mbar_wait(x_ready_bar, x_phase)) {
+            fail(3);
+            break;
+          }
+          x_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_gram = make_idesc(1u, false, false, 128, 128);  // K-major x K-major
+      const uint32_t idesc_sx = make_idesc(1u, false, true, 128, 64);      // S K-major, X box MN-major
+      const uint32_t a_addr = smem_u32(a_buf), s_addr = smem_u32(s_buf);
+      int unit = 0;
+      uint32_t uphase = 0;
+      int ab = 0;
+      uint32_t aphase = 0, a_phase = 0, s_phase = 0;
+      int mq = 0;
+      uint32_t mq_phase = 0;
+      bool ok = true;
+      auto next_acc = [&]() {
+        if (++ab == 2) {
+          ab = 0;
+          aphase ^= 1u;
+        }
+      };
+      auto wait_unit = [&]() -> bool {
+        if (!mbar_wait(&full_bar[unit], uphase)) {
+          fail(4);
+          return false;
+        }
+        tc_fence_after();
+        return true;
+      };
+      auto release_unit = [&]() {
+        umma_commit(&empty_bar[unit]);
+        if (++unit == kSmallUnits) {
+          unit = 0;
+          uphase ^= 1u;
+        }
+      };
+      while (ok) {
+        if (!mbar_wait(&mq_full_bar[mq], mq_phase)) {
+          fail(5);
+          break;
+        }
+        const int b = mat_queue[mq];
+        mbar_arrive(&mq_empty_bar[mq]);
+        if (++mq == 2) {
+          mq = 0;
+          mq_phase ^= 1u;
+        }
+        if (b < 0) break;
+        for (int it = 0; it < p.steps && ok; ++it) {
+          const bool quintic = p.abc[3 * it + 2] != 0.0f;
+          // ---- Gram
+          if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+            fail(6);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          uint32_t acc = tmem_base + static_cast<uint32_t>(ab * 256);
+          for (int kb = 0; kb < nk && ok; ++kb) {
+            ok = wait_unit();
+            if (!ok) break;
+            const uint32_t u = smem_u32(ring + unit * kSmallUnitBytes);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t d = make_smem_desc(u + k * 32u, 0u, 1024u);
+              umma_f16(acc, d, d, idesc_gram, (kb | k) != 0 ? 1u : 0u);
+            }
+            release_unit();
+          }
+          if (!ok) break;
+          umma_commit(&acc_full_bar[ab]);
+          next_acc();
+          // ---- A^2 (quintic steps only)
+          if (quintic) {
+            if (!mbar_wait(a_ready_bar, a_phase)) {
+              fail(7);
+              ok = false;
+              break;
+            }
+            if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+              fail(6);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            acc = tmem_base + static_cast<uint32_t>(ab * 256);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint64_t d = make_smem_desc(a_addr + (k >> 2) * kSmallUnitBytes + (k & 3) * 32u, 0u, 1024u);
+              umma_f16(acc, d, d, idesc_gram, k != 0 ? 1u : 0u);
+            }
+            umma_commit(&acc_full_bar[ab]);
+            next_acc();
+          }
+          a_phase ^= 1u;
+          // ---- S X (S is A itself on cubic steps)
+          if (!mbar_wait(s_ready_bar, s_phase)) {
+            fail(8);
+            ok = false;
+            break;
+          }
+          s_phase ^= 1u;
+          const uint32_t s_op = quintic ? s_addr : a_addr;
+          for (int t = 0; t < nt && ok; ++t) {
+            if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+              fail(6);
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            acc = tmem_base + static_cast<uint32_t>(ab * 256);
+            for (int q = 0; q < 4 && ok; ++q) {
+              ok = wait_unit();
+              if (!ok) break;
+              const uint32_t u = smem_u32(ring + unit * kSmallUnitBytes);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const uint64_t da = make_smem_desc(s_op + (k >> 2) * kSmallUnitBytes + (k & 3) * 32u, 0u, 1024u);
+                const uint64_t db = make_smem_desc(u + k * 2048u, 0u, 1024u);
+                umma_f16(acc + static_cast<uint32_t>(q * 64), da, db, idesc_sx, k != 0 ? 1u : 0u);
+              }
+              release_unit();
+            }
+            if (!ok) break;
+            umma_commit(&acc_full_bar[ab]);
+            next_acc();
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int quarter = warp & 3;
+    const int chunk0 = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    int ab = 0;
+    uint32_t aphase = 0;
+    int mq = 0;
+    uint32_t mq_phase = 0;
+    bool ok = true;
+    auto next_acc = [&]() {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty_bar[ab]);
+      if (++ab == 2) {
+        ab = 0;
+        aphase ^= 1u;
+      }
+    };
+    auto load_chunk = [&](int c, uint32_t (&acc)[32]) {
+      __syncwarp();
+      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * 256 + c * 32),
+                    acc);
+      tmem_ld_wait();
+    };
+    while (ok) {
+      if (!mbar_wait(&mq_full_bar[mq], mq_phase)) {
+        fail(9);
+        break;
+      }
+      const int b = mat_queue[mq];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&mq_empty_bar[mq]);
+      if (++mq == 2) {
+        mq = 0;
+        mq_phase ^= 1u;
+      }
+      if (b < 0) break;
+      for (int it = 0; it < p.steps && ok; ++it) {
+        const float ca = p.abc[3 * it], cb = p.abc[3 * it + 1], cc = p.abc[3 * it + 2];
+        const bool quintic = cc != 0.0f;
+        const bool last = (it == p.steps - 1);
+        // ---- Gram epilogue: A (bf16) into shared memory, operand layout
+        if (!mbar_wait(&acc_full_bar[ab], aphase)) {
+          fail(10);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int c = chunk0; c < 4; c += 2) {
+          uint32_t acc[32];
+          load_chunk(c, acc);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            unsigned int w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const unsigned int lo = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(acc[8 * q + 2 * e])));
+              const unsigned int hi = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(acc[8 * q + 2 * e + 1])));
+              w[e] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(a_buf + swz_offset(row, c * 32 + q * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(a_ready_bar);
+          if (!quintic) mbar_arrive(s_ready_bar);  // cubic step: S is A
+        }
+        next_acc();
+        // ---- A^2 epilogue: S = b A + c A^2 into shared memory
+        if (quintic) {
+          if (!mbar_wait(&acc_full_bar[ab], aphase)) {
+            fail(10);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          for (int c = chunk0; c < 4; c += 2) {
+            uint32_t acc[32];
+            load_chunk(c, acc);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 av = *reinterpret_cast<const uint4*>(a_buf + swz_offset(row, c * 32 + q * 8));
+              const unsigned int aw[4] = {av.x, av.y, av.z, av.w};
+              unsigned int w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a0 = __uint_as_float(aw[e] << 16), a1 = __uint_as_float(aw[e] & 0xFFFF0000u);
+                const float v0 = fmaf(cb, a0, cc * __uint_as_float(acc[8 * q + 2 * e]));
+                const float v1 = fmaf(cb, a1, cc * __uint_as_float(acc[8 * q + 2 * e + 1]));
+                w[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v0))) |
+                       (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v1))) << 16);
+              }
+              *reinterpret_cast<uint4*>(s_buf + swz_offset(row, c * 32 + q * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_ready_bar);
+          next_acc();
+        }
+        // ---- S X epilogue: X' = a X + alpha (S X), alpha = 1 (quintic) or b (cubic)
+        const float alpha = quintic ? 1.0f : cb;
+        const int src = it & 1, dst = src ^ 1;
+        const unsigned short* xin = p.buf[src] + static_cast<long long>(b) * p.stride[src];
+        unsigned short* xout = p.buf[dst] + static_cast<long long>(b) * p.stride[dst];
+        for (int t = 0; t < nt && ok; ++t) {
+          if (!mbar_wait(&acc_full_bar[ab], aphase)) {
+            fail(10);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          for (int c = chunk0; c < 8; c += 2) {
+            const int col0 = t * 256 + c * 32;
+            if (col0 >= p.n) break;
+            uint32_t acc[32];
+            load_chunk(c, acc);
+            if (row >= p.m) continue;
+            const int ncols = min(32, p.n - col0);
+            const unsigned short* cin = xin + static_cast<long long>(row) * p.ld[src] + col0;
+            float v[32];
+            if (ncols == 32) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 t4 = __ldcg(reinterpret_cast<const uint4*>(cin) + q);  // written earlier by this kernel: L2, not L1
+                const unsigned int ws[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  v[8 * q + 2 * e] = fmaf(ca, __uint_as_float(ws[e] << 16), alpha * __uint_as_float(acc[8 * q + 2 * e]));
+                  v[8 * q + 2 * e + 1] =
+                      fmaf(ca, __uint_as_float(ws[e] & 0xFFFF0000u), alpha * __uint_as_float(acc[8 * q + 2 * e + 1]));
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncols)
+                  v[j] = fmaf(ca, __uint_as_float(static_cast<unsigned int>(__ldcg(cin + j)) << 16), alpha * __uint_as_float(acc[j]));
+            }
+            if (last) {
+              if (p.out_fp32) {
+                float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(b) * p.strideo +
+                           static_cast<long long>(row) * p.ldo + col0;
+                if (ncols == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+                  for (int q = 0; q < 8; ++q)
+                    reinterpret_cast<float4*>(o)[q] = make_float4(__bfloat162float(__float2bfloat16_rn(v[4 * q])),
+                                                                  __bfloat162float(__float2bfloat16_rn(v[4 * q + 1])),
+                                                                  __bfloat162float(__float2bfloat16_rn(v[4 * q + 2])),
+                                                                  __bfloat162float(__float2bfloat16_rn(v[4 * q + 3])));
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (j < ncols) o[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+                }
+              } else {
+                unsigned short* o = reinterpret_cast<unsigned short*>(p.out) + static_cast<long long>(b) * p.strideo +
+                                    static_cast<long long>(row) * p.ldo + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) o[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
+              }
+            } else {
+              unsigned short* o = xout + static_cast<long long>(row) * p.ld[dst] + col0;
+              if (ncols == 32) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  unsigned int w[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    w[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e]))) |
+                           (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e + 1]))) << 16);
+                  reinterpret_cast<uint4*>(o)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) o[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
+              }
+            }
+          }
+          // Make this warp's part of the next iterate visible to the TMA reads of the next iteration.
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(x_ready_bar);
+          next_acc();
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace eo

@@ -227,16 +227,19 @@ int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int u
  * stride `stride` (multiples of 8, 16-byte-aligned base); the iteration runs on the wide orientation
  * (on X^T, without copying, when rows > cols).  The last step writes `out` (bf16, or fp32 = bf16-rounded
  * values widened, with ldo / strideo); X is used as a ping-pong buffer and is clobbered when steps > 1.
- * `use_syrk` selects the lower-triangular kernel for A and S (falls back to the general kernel when
- * rows or cols is not a multiple of 8).  `host_abc` is a host array of 3 * steps floats.
+ * `flags`: bit 0 selects the lower-triangular kernel for A and S (falls back to the general kernel when rows
+ * or cols is not a multiple of 8); bit 1 disables the fused small-matrix kernel.  That kernel is used for
+ * batches of wide matrices with rows <= 128 (per-head / split-QKV blocks, cols >= 256, steps <= 16): one
+ * persistent kernel runs every iteration of a matrix with A, A^2 and S kept in shared memory, reading the
+ * iterate twice and writing it once per iteration.  `host_abc` is a host array of 3 * steps floats.
  * `workspace`: eo_newton_schulz_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
  *
  * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 with
- * the step functions of :348-476; launches 3 * steps (2 * steps when c == 0) kernels.
+ * the step functions of :348-476; launches 3 * steps (2 * steps when c == 0) kernels, or one.
  */
 size_t eo_newton_schulz_workspace_bytes(int batch, int rows, int cols);
 int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
-                          int steps, int use_syrk, void* out, int out_fp32, int64_t ldo, int64_t strideo,
+                          int steps, int flags, void* out, int out_fp32, int64_t ldo, int64_t strideo,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*

@@ -194,6 +194,24 @@ def test_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
         assert fast.shape == slow.shape and torch.equal(fast, slow)
 
 
+@pytest.mark.parametrize(
+    "shape", [(4, 128, 512), (3, 64, 1024), (2, 128, 8192), (5, 120, 520), (128, 4096), (300, 128, 256), (1, 8, 256)]
+)
+@pytest.mark.parametrize("ctype,steps", [("simple", 5), ("cubic5", 5), ("polar_express", 1), ("quintic", 2)])
+def test_fused_small_matrix_kernel_equals_general_kernels(shape, ctype, steps, monkeypatch):
+    """Matrices with at most 128 rows run all iterations in one persistent kernel that keeps A, A^2 and S in shared
+    memory; same products, same rounding points, so the result must equal the general kernels' bit for bit."""
+    x = randn_tensor(*shape, seed=41, scale=1e-3)
+    with fp32_matmul_precision("medium"):
+        fused = muon_utils.newton_schulz(x, steps, ctype, use_syrk=True)
+        monkeypatch.setattr(nat, "FUSED_SMALL_MATRICES", False)
+        general = muon_utils.newton_schulz(x, steps, ctype, use_syrk=True)
+    assert fused.dtype == torch.float32 and fused.shape == general.shape
+    assert torch.equal(fused, general)
+    ref = newton_schulz_torch(x, steps, ctype, bf16=True)
+    assert rel_fro(fused, ref) <= BF16_TOL
+
+
 def test_muon_steps_match_reference_golden(golden_dir):
     data = np.load(os.path.join(golden_dir, "muon_steps.npz"))
     with open(os.path.join(golden_dir, "muon_cases.json")) as f:
