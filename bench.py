@@ -218,9 +218,15 @@ def run_gpu_arm(args) -> None:
     x_host = torch.empty(M, N_COLS, dtype=torch.float32).pin_memory()
     # Same distribution as config 4 (N(0,1)); generated in row blocks to bound host memory traffic.
     for r0 in range(0, M, 1024):
-        x_host[r0 : r0 + 1024].copy_(torch.randn(1024, N_COLS, generator=g, dtype=torch.float32))
+        r1 = min(r0 + 1024, M)
+        x_host[r0:r1].copy_(torch.randn(r1 - r0, N_COLS, generator=g, dtype=torch.float32))
     x = x_host.to(dev, non_blocking=True)
     torch.cuda.synchronize()
+    if args.batch > 0:
+        if not args.kernels_only:
+            raise SystemExit("--batch needs --kernels-only")
+        gb = torch.Generator(device=dev).manual_seed(4)
+        x = torch.randn(args.batch, M, N_COLS, generator=gb, device=dev) * 1e-3
 
     # Exchange buffer of the layer-parallel scheme: symmetric memory written by copy engines (no SMs taken from the
     # persistent tensor-core kernels); NCCL all-gather if symmetric memory cannot be set up on this box.
@@ -290,8 +296,10 @@ def run_gpu_arm(args) -> None:
     if args.kernels_only:
         if rank == 0:
             dense, sym = flops(M, N_COLS, NS_STEPS)
-            print(json.dumps({"kernels_only": True, "shape": [M, N_COLS], "ms_per_step": ms_total / args.steps,
-                              "tflops_dense_eq": dense * args.steps / (ms_total / 1e3) / 1e12,
+            nb = max(args.batch, 1)
+            print(json.dumps({"kernels_only": True, "shape": [M, N_COLS], "batch": args.batch,
+                              "ms_per_step": ms_total / args.steps,
+                              "tflops_dense_eq": nb * dense * args.steps / (ms_total / 1e3) / 1e12,
                               "gpu_launches": launches, "device_status": _native.read_device_status(dev)}), flush=True)
         if world > 1:
             dist.barrier()
@@ -574,6 +582,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shape", type=int, nargs=2, default=None, metavar=("M", "N"),
                     help="matrix shape instead of 8192 28672 (for profiler captures of a small case)")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="with --kernels-only: run on a (BATCH, M, N) stack of matrices (per-head workload)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="device-resident timing only: no end-to-end loop, CPU baseline or clock sampling, and "
                     "--warmup taken as given (for profiler captures; not a benchmark number)")

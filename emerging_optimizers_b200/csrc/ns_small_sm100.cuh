@@ -7,11 +7,13 @@
 //   Gram   : X streamed through a shared-memory ring in 128 x 64 boxes (K-major), accumulated in TMEM;
 //            the epilogue rounds A to bf16 and writes it into shared memory in the 128B-swizzled operand layout
 //   A^2    : tcgen05.mma on the shared-memory copy of A (skipped when c == 0); epilogue writes S likewise
-//   S X    : X streamed again, 128 x 256 output tiles (the same boxes now act as MN-major B operands, four
-//            N = 64 MMAs per k-step), epilogue adds a X and writes the next iterate to global memory
+//   S X    : X streamed again, 128 x 128 output tiles (the same boxes now act as MN-major B operands, two
+//            N = 64 MMAs per k-step); the epilogue takes the a X term from the boxes still sitting in the ring,
+//            overwrites them in place with the new iterate and a store warp sends them out with TMA stores
+//            (no scattered global loads or stores)
 //
 // so per iteration a matrix is read twice and written once, with no launch boundary, no global A / S traffic and
-// no per-launch tail.  Roles as in the general kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue.
+// no per-launch tail.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue, warp 10 TMA stores.
 // Every wait is bounded; a wait that runs out records a code in the status word and the CTA drains.
 #pragma once
 
@@ -24,9 +26,11 @@ namespace eo {
 constexpr int kSmallUnitBytes = 128 * 128;  // one TMA box: 128 rows x 64 bf16
 constexpr int kSmallUnits = 10;             // ring depth
 constexpr int kSmallABytes = 2 * kSmallUnitBytes;  // 128 x 128 bf16 operand (two 64-column atoms)
-constexpr int kSmallThreads = 64 + 32 * 8;
+constexpr int kSmallThreads = 64 + 32 * 8 + 32;
 constexpr int kSmallSmemBytes = kSmallUnits * kSmallUnitBytes + 2 * kSmallABytes + 1024 + 1024;
 constexpr int kSmallMaxSteps = 16;
+constexpr int kSmallAcc = 4;       // TMEM accumulators of 128 columns each, used round-robin by every product
+constexpr int kSmallTileN = 128;   // output tile width of the S X product
 constexpr uint32_t kStatusSmall = 0x50u;
 
 struct SmallParams {
@@ -62,12 +66,13 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_buf + kSmallABytes);
   uint64_t* full_bar = bars;                       // [kSmallUnits]
   uint64_t* empty_bar = full_bar + kSmallUnits;    // [kSmallUnits]
-  uint64_t* acc_full_bar = empty_bar + kSmallUnits;  // [2]
-  uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2]
-  uint64_t* a_ready_bar = acc_empty_bar + 2;         // A written to shared memory
+  uint64_t* acc_full_bar = empty_bar + kSmallUnits;  // [kSmallAcc]
+  uint64_t* acc_empty_bar = acc_full_bar + kSmallAcc;  // [kSmallAcc]
+  uint64_t* a_ready_bar = acc_empty_bar + kSmallAcc;   // A written to shared memory
   uint64_t* s_ready_bar = a_ready_bar + 1;           // S written to shared memory
   uint64_t* x_ready_bar = s_ready_bar + 1;           // every tile of the next iterate written to global memory
-  uint64_t* mq_full_bar = x_ready_bar + 1;           // [2] matrix-index queue
+  uint64_t* st_ready_bar = x_ready_bar + 1;          // [kSmallAcc] output tile complete in the ring units
+  uint64_t* mq_full_bar = st_ready_bar + kSmallAcc;  // [2] matrix-index queue
   uint64_t* mq_empty_bar = mq_full_bar + 2;          // [2]
   int* mat_queue = reinterpret_cast<int*>(mq_empty_bar + 2);  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mat_queue + 2);
@@ -75,22 +80,25 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nk = (p.n + 63) / 64;      // Gram k-blocks
-  const int nt = (p.n + 255) / 256;    // output tiles of the S X product
+  const int nt = (p.n + kSmallTileN - 1) / kSmallTileN;  // output tiles of the S X product
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSmallUnits; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSmallAcc; ++s) {
       mbar_init(&acc_full_bar[s], 1);
       mbar_init(&acc_empty_bar[s], 8);
+      mbar_init(&st_ready_bar[s], 8);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&mq_full_bar[s], 1);
-      mbar_init(&mq_empty_bar[s], 9);
+      mbar_init(&mq_empty_bar[s], 10);  // MMA thread, eight epilogue warps, store thread
     }
     mbar_init(a_ready_bar, 8);
     mbar_init(s_ready_bar, 8);
-    mbar_init(x_ready_bar, 8u * static_cast<uint32_t>(nt));
+    mbar_init(x_ready_bar, 1);
     mbar_init_fence();
     tma_prefetch_desc(&maps.x[0]);
     tma_prefetch_desc(&maps.x[1]);
@@ -156,9 +164,9 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           }
           for (int kb = 0; kb < nk && ok; ++kb) ok = load_unit(map, kb * 64, b);
           for (int t = 0; t < nt && ok; ++t)
-            for (int q = 0; q < 4 && ok; ++q) ok = load_unit(map, t * 256 + q * 64, b);
+            for (int q = 0; q < 2 && ok; ++q) ok = load_unit(map, t * kSmallTileN + q * 64, b);
         }
-        // The output tiles of the last iteration also arrive on x_ready: consume that phase.
+        // The epilogue warps also arrive on x_ready after the last iteration: consume that phase.
         if (ok && p.steps > 0) {
           if (!mbar_wait(x_ready_bar, x_phase)) {
             fail(3);
@@ -182,7 +190,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
       uint32_t mq_phase = 0;
       bool ok = true;
       auto next_acc = [&]() {
-        if (++ab == 2) {
+        if (++ab == kSmallAcc) {
           ab = 0;
           aphase ^= 1u;
         }
@@ -223,7 +231,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
             break;
           }
           tc_fence_after();
-          uint32_t acc = tmem_base + static_cast<uint32_t>(ab * 256);
+          uint32_t acc = tmem_base + static_cast<uint32_t>(ab * 128);
           for (int kb = 0; kb < nk && ok; ++kb) {
             ok = wait_unit();
             if (!ok) break;
@@ -240,10 +248,12 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           next_acc();
           // ---- A^2 (quintic steps only)
           if (quintic) {
-            if (!mbar_wait(a_ready_bar, a_phase)) {
-              fail(7);
-              ok = false;
-              break;
+            {
+              if (!mbar_wait(a_ready_bar, a_phase)) {
+                fail(7);
+                ok = false;
+                break;
+              }
             }
             if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
               fail(6);
@@ -251,7 +261,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
               break;
             }
             tc_fence_after();
-            acc = tmem_base + static_cast<uint32_t>(ab * 256);
+            acc = tmem_base + static_cast<uint32_t>(ab * 128);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint64_t d = make_smem_desc(a_addr + (k >> 2) * kSmallUnitBytes + (k & 3) * 32u, 0u, 1024u);
@@ -262,22 +272,26 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           }
           a_phase ^= 1u;
           // ---- S X (S is A itself on cubic steps)
-          if (!mbar_wait(s_ready_bar, s_phase)) {
-            fail(8);
-            ok = false;
-            break;
+          {
+            if (!mbar_wait(s_ready_bar, s_phase)) {
+              fail(8);
+              ok = false;
+              break;
+            }
           }
           s_phase ^= 1u;
           const uint32_t s_op = quintic ? s_addr : a_addr;
           for (int t = 0; t < nt && ok; ++t) {
-            if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
-              fail(6);
-              ok = false;
-              break;
+            {
+              if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+                fail(6);
+                ok = false;
+                break;
+              }
             }
             tc_fence_after();
-            acc = tmem_base + static_cast<uint32_t>(ab * 256);
-            for (int q = 0; q < 4 && ok; ++q) {
+            acc = tmem_base + static_cast<uint32_t>(ab * 128);
+            for (int q = 0; q < 2 && ok; ++q) {
               ok = wait_unit();
               if (!ok) break;
               const uint32_t u = smem_u32(ring + unit * kSmallUnitBytes);
@@ -287,7 +301,11 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
                 const uint64_t db = make_smem_desc(u + k * 2048u, 0u, 1024u);
                 umma_f16(acc + static_cast<uint32_t>(q * 64), da, db, idesc_sx, k != 0 ? 1u : 0u);
               }
-              release_unit();
+              // not released here: the epilogue reuses the unit, the store warp frees it
+              if (++unit == kSmallUnits) {
+                unit = 0;
+                uphase ^= 1u;
+              }
             }
             if (!ok) break;
             umma_commit(&acc_full_bar[ab]);
@@ -296,13 +314,14 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         }
       }
     }
-  } else {
+  } else if (warp < 10) {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;
     const int chunk0 = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     int ab = 0;
     uint32_t aphase = 0;
+    int unit = 0;  // ring position of the next unit, advanced exactly as the producer and the MMA thread do
     int mq = 0;
     uint32_t mq_phase = 0;
     bool ok = true;
@@ -310,14 +329,14 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[ab]);
-      if (++ab == 2) {
+      if (++ab == kSmallAcc) {
         ab = 0;
         aphase ^= 1u;
       }
     };
     auto load_chunk = [&](int c, uint32_t (&acc)[32]) {
       __syncwarp();
-      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * 256 + c * 32),
+      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * 128 + c * 32),
                     acc);
       tmem_ld_wait();
     };
@@ -401,44 +420,51 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         }
         // ---- S X epilogue: X' = a X + alpha (S X), alpha = 1 (quintic) or b (cubic)
         const float alpha = quintic ? 1.0f : cb;
-        const int src = it & 1, dst = src ^ 1;
-        const unsigned short* xin = p.buf[src] + static_cast<long long>(b) * p.stride[src];
-        unsigned short* xout = p.buf[dst] + static_cast<long long>(b) * p.stride[dst];
+        unit = (unit + nk) % kSmallUnits;  // the Gram phase consumed nk units
         for (int t = 0; t < nt && ok; ++t) {
+          const int u0 = unit, u1 = (unit + 1 == kSmallUnits) ? 0 : unit + 1;
+          unit = (u1 + 1 == kSmallUnits) ? 0 : u1 + 1;
           if (!mbar_wait(&acc_full_bar[ab], aphase)) {
             fail(10);
             ok = false;
             break;
           }
           tc_fence_after();
-          for (int c = chunk0; c < 8; c += 2) {
-            const int col0 = t * 256 + c * 32;
-            if (col0 >= p.n) break;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int c = chunk0 + 2 * h;  // 32-column chunk of the 128-column tile
+            const int col0 = t * kSmallTileN + c * 32;
             uint32_t acc[32];
             load_chunk(c, acc);
-            if (row >= p.m) continue;
-            const int ncols = min(32, p.n - col0);
-            const unsigned short* cin = xin + static_cast<long long>(row) * p.ld[src] + col0;
+            // The tile's X values sit in the ring unit the MMA just read (rows = matrix rows, 64 columns per unit,
+            // 16-byte groups XOR-swizzled by the row): read a X from there, write the new iterate back in place.
+            uint8_t* urow = ring + ((c < 2) ? u0 : u1) * kSmallUnitBytes + row * 128;
+            const int g0 = (c & 1) * 4;
             float v[32];
-            if (ncols == 32) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 xv = *reinterpret_cast<const uint4*>(urow + (((g0 + q) ^ (row & 7)) << 4));
+              const unsigned int ws[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                v[8 * q + 2 * e] = fmaf(ca, __uint_as_float(ws[e] << 16), alpha * __uint_as_float(acc[8 * q + 2 * e]));
+                v[8 * q + 2 * e + 1] =
+                    fmaf(ca, __uint_as_float(ws[e] & 0xFFFF0000u), alpha * __uint_as_float(acc[8 * q + 2 * e + 1]));
+              }
+            }
+            if (!last) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const uint4 t4 = __ldcg(reinterpret_cast<const uint4*>(cin) + q);  // written earlier by this kernel: L2, not L1
-                const unsigned int ws[4] = {t4.x, t4.y, t4.z, t4.w};
+                unsigned int w[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  v[8 * q + 2 * e] = fmaf(ca, __uint_as_float(ws[e] << 16), alpha * __uint_as_float(acc[8 * q + 2 * e]));
-                  v[8 * q + 2 * e + 1] =
-                      fmaf(ca, __uint_as_float(ws[e] & 0xFFFF0000u), alpha * __uint_as_float(acc[8 * q + 2 * e + 1]));
-                }
+                for (int e = 0; e < 4; ++e)
+                  w[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e]))) |
+                         (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e + 1]))) << 16);
+                *reinterpret_cast<uint4*>(urow + (((g0 + q) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
               }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncols)
-                  v[j] = fmaf(ca, __uint_as_float(static_cast<unsigned int>(__ldcg(cin + j)) << 16), alpha * __uint_as_float(acc[j]));
-            }
-            if (last) {
+            } else if (row < p.m && col0 < p.n) {
+              // last iteration: the result leaves in its final dtype, straight from registers
+              const int ncols = min(32, p.n - col0);
               if (p.out_fp32) {
                 float* o = reinterpret_cast<float*>(p.out) + static_cast<long long>(b) * p.strideo +
                            static_cast<long long>(row) * p.ldo + col0;
@@ -457,35 +483,82 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
               } else {
                 unsigned short* o = reinterpret_cast<unsigned short*>(p.out) + static_cast<long long>(b) * p.strideo +
                                     static_cast<long long>(row) * p.ldo + col0;
+                if (ncols == 32 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (j < ncols) o[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
-              }
-            } else {
-              unsigned short* o = xout + static_cast<long long>(row) * p.ld[dst] + col0;
-              if (ncols == 32) {
+                  for (int q = 0; q < 4; ++q) {
+                    unsigned int w[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  unsigned int w[4];
+                    for (int e = 0; e < 4; ++e)
+                      w[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e]))) |
+                             (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e + 1]))) << 16);
+                    reinterpret_cast<uint4*>(o)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                  }
+                } else {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e)
-                    w[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e]))) |
-                           (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v[8 * q + 2 * e + 1]))) << 16);
-                  reinterpret_cast<uint4*>(o)[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                  for (int j = 0; j < 32; ++j)
+                    if (j < ncols) o[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
                 }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (j < ncols) o[j] = __bfloat16_as_ushort(__float2bfloat16_rn(v[j]));
               }
             }
           }
-          // Make this warp's part of the next iterate visible to the TMA reads of the next iteration.
-          __threadfence();
-          asm volatile("fence.proxy.async;" ::: "memory");
+          // Hand the tile (now holding the new iterate) to the store warp, then free the accumulator.
+          fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(x_ready_bar);
+          if (lane == 0) mbar_arrive(&st_ready_bar[ab]);
           next_acc();
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ store warp (warp 10)
+    if (elect_one()) {
+      int unit = 0, sb = 0;
+      uint32_t st_bits = 0;  // phase parity of each st_ready barrier (only S X tiles complete their phases)
+      int mq = 0;
+      uint32_t mq_phase = 0;
+      bool ok = true;
+      while (ok) {
+        if (!mbar_wait(&mq_full_bar[mq], mq_phase)) {
+          fail(11);
+          break;
+        }
+        const int b = mat_queue[mq];
+        mbar_arrive(&mq_empty_bar[mq]);
+        if (++mq == 2) {
+          mq = 0;
+          mq_phase ^= 1u;
+        }
+        if (b < 0) break;
+        for (int it = 0; it < p.steps && ok; ++it) {
+          const bool quintic = p.abc[3 * it + 2] != 0.0f;
+          const bool last = (it == p.steps - 1);
+          const CUtensorMap* map = &maps.x[(it + 1) & 1];
+          // accumulator rotation: Gram, (A^2), then one per tile; ring rotation: nk Gram units, then two per tile
+          sb = (sb + (quintic ? 2 : 1)) % kSmallAcc;
+          unit = (unit + nk) % kSmallUnits;
+          for (int t = 0; t < nt && ok; ++t) {
+            if (!mbar_wait(&st_ready_bar[sb], (st_bits >> sb) & 1u)) {
+              fail(12);
+              ok = false;
+              break;
+            }
+            st_bits ^= (1u << sb);
+            if (++sb == kSmallAcc) sb = 0;
+            const int u0 = unit, u1 = (unit + 1 == kSmallUnits) ? 0 : unit + 1;
+            unit = (u1 + 1 == kSmallUnits) ? 0 : u1 + 1;
+            if (!last) {
+              tma_store_3d(map, ring + u0 * kSmallUnitBytes, t * kSmallTileN, 0, b);
+              tma_store_3d(map, ring + u1 * kSmallUnitBytes, t * kSmallTileN + 64, 0, b);
+              tma_store_commit();
+              tma_store_wait_read0();  // shared memory has been read: the units may be refilled
+            }
+            mbar_arrive(&empty_bar[u0]);
+            mbar_arrive(&empty_bar[u1]);
+          }
+          if (!ok) break;
+          // Every store of this iteration has landed in global memory: the producer may read the iterate back.
+          tma_store_wait0();
+          mbar_arrive(x_ready_bar);
         }
       }
     }
