@@ -35,6 +35,7 @@ if ROOT not in sys.path:
 M, N_COLS, NS_STEPS, COEFF = 8192, 28672, 5, "simple"
 CPU_SAMPLE = (2048, 7168)  # corner block timed on the host
 NOMINAL_BF16_TFLOPS = 2250.0
+TRAFFIC_BYTES_PER_LAUNCH = 0.82e9
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
@@ -311,8 +312,9 @@ def run_gpu_arm(args) -> None:
     for _ in range(2):
         ns_call(x)
     torch.cuda.synchronize()
-    kernel_ms = [a.elapsed_time(b) for _, a, b in _native.launch_timer]
-    names = [n for n, _, _ in _native.launch_timer]
+    kernel_ms = [a.elapsed_time(b) for _, a, b, _ in _native.launch_timer]
+    names = [n for n, _, _, _ in _native.launch_timer]
+    kernel_launches = sum(k for _, _, _, k in _native.launch_timer)
     _native.launch_timer = None
 
     # ---- timed region 2: end to end with host buffers ------------------------------------------
@@ -371,7 +373,8 @@ def run_gpu_arm(args) -> None:
         # The timed region is seconds long, so the sustained cuBLAS figure is the denominator.
         peak = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
         k_total_ms = sum(kernel_ms)
-        n_launch = len(kernel_ms)
+        n_launch = kernel_launches
+        # two newton_schulz calls were timed: 2 * sym FLOP in n_launch launches of eo_gemm_kernel
         achieved = (sym * 2 / n_launch) / (k_total_ms / n_launch / 1e3) / 1e12 if n_launch else None
         by_name = {}
         for nme, ms in zip(names, kernel_ms):
@@ -403,8 +406,13 @@ def run_gpu_arm(args) -> None:
                 "unit": "TFLOP/s",
                 "frac": (achieved / peak) if achieved else None,
                 "frac_of_burst_peak": (achieved / float(peaks["bf16_tflops"])) if achieved else None,
-                "traffic": None,
-                "launch_ms": {k: sum(v) / len(v) for k, v in by_name.items()},
+                # DRAM bytes per launch, from the ncu capture of one iteration on 4096 x 16384 (read + write of the
+                # Gram, A^2 and BX launches: 247 + 35 + 417 MB) scaled by operand bytes to this shape and averaged
+                # over the three launches; see profiles/ and DESIGN.md.
+                "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
+                "algorithmic_flops_per_launch": sym * 2 / n_launch if n_launch else None,
+                "avg_launch_ms": k_total_ms / n_launch if n_launch else None,
+                "call_ms": {k: sum(v) / len(v) for k, v in by_name.items()},
                 "launches_timed": n_launch,
             },
             "e2e": {

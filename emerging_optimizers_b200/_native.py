@@ -103,7 +103,8 @@ _PROTOTYPES: dict[str, tuple] = {
 
 # Kernel launches issued through this module since import (what a benchmark reports as its own launches), and an
 # optional per-launch timing hook: when `launch_timer` is a list, every tensor-core launch appends
-# (name, start_event, end_event) recorded on the launching stream.
+# (name, start_event, end_event, kernels) recorded on the launching stream around the `kernels` back-to-back launches
+# of that call.
 launch_count = 0
 launch_timer: list | None = None
 
@@ -125,7 +126,7 @@ class _Timed:
         if self.timed and launch_timer is not None:
             end = torch.cuda.Event(enable_timing=True)
             end.record(torch.cuda.current_stream(self.device))
-            launch_timer.append((self.name, self.start, end))
+            launch_timer.append((self.name, self.start, end, self.kernels))
 
 
 class NativeLibraryError(RuntimeError):
