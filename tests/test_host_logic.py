@@ -249,3 +249,30 @@ def test_precision_context_and_pg_helpers():
         assert torch.get_float32_matmul_precision() == "medium"
     assert torch.get_float32_matmul_precision() == before
     assert get_pg_size(None) == 1 and get_pg_rank(None) == 0
+
+
+def test_fused_step_batch_plan_groups_equal_shapes_within_a_byte_budget():
+    from emerging_optimizers_b200.orthogonalized_optimizers import _fused_step
+
+    shapes = [(4096, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (1024, 4096), (40, 24)]
+    batches = _fused_step.plan_batches(shapes)
+    assert sorted(i for b in batches for i in b) == list(range(len(shapes)))
+    for b in batches:
+        assert len({shapes[i] for i in b}) == 1
+    assert [0, 2] in batches and [1, 4] in batches
+    # a budget of one matrix splits a group into single-matrix batches
+    small = _fused_step.plan_batches(shapes, max_batch_bytes=2 * 4096 * 4096)
+    assert [0] in small and [2] in small and [1, 4] in small
+    # CPU tensors are never eligible for the fused kernels
+    p = torch.zeros(8, 8)
+    assert not _fused_step.eligible(p, torch.zeros(8, 8))
+    assert not _fused_step.eligible(p, None)
+
+
+def test_tp_exchange_is_chosen_by_group_size(monkeypatch):
+    from emerging_optimizers_b200.distributed import tensor_parallel as tp
+
+    x = torch.zeros(8, 8, dtype=torch.bfloat16)
+    assert not tp.fused_gram_available(x, None)
+    assert not tp.fused_gram_available(x, object())  # CPU tensor: never
+    assert tp.FUSED_MAX_WORLD == 4
