@@ -43,13 +43,17 @@ def eligible(p: torch.Tensor, g: torch.Tensor | None) -> bool:
     )
 
 
-def plan_batches(shapes: Sequence[tuple[int, int]], max_batch_bytes: int = MAX_BATCH_BYTES) -> list[list[int]]:
-    """Group indices of equally shaped matrices, in order of first appearance, into batches of bounded size."""
-    by_shape: dict[tuple[int, int], list[int]] = {}
+def plan_batches(
+    shapes: Sequence[tuple[int, int]], max_batch_bytes: int = MAX_BATCH_BYTES, devices: Sequence | None = None
+) -> list[list[int]]:
+    """Group indices of equally shaped matrices (on the same device), in order of first appearance, into batches of
+    bounded size."""
+    by_shape: dict[tuple, list[int]] = {}
     for i, s in enumerate(shapes):
-        by_shape.setdefault(tuple(s), []).append(i)
+        key = (tuple(s), None if devices is None else devices[i])
+        by_shape.setdefault(key, []).append(i)
     batches: list[list[int]] = []
-    for shape, idx in by_shape.items():
+    for (shape, _), idx in by_shape.items():
         per = max(1, max_batch_bytes // max(1, 2 * shape[0] * shape[1]))
         for k in range(0, len(idx), per):
             batches.append(idx[k : k + per])
@@ -86,7 +90,7 @@ def orthogonalized_updates(
     schedule = list(muon_utils.get_coefficient_iterator(steps, sets, mode=mode))
 
     out: list[torch.Tensor | None] = [None] * len(params)
-    for batch in plan_batches([tuple(p.shape) for p in params], max_batch_bytes):
+    for batch in plan_batches([tuple(p.shape) for p in params], max_batch_bytes, [p.device for p in params]):
         rows, cols = params[batch[0]].shape
         dev = params[batch[0]].device
         # Row stride padded to 16 bytes so that TMA can address shapes like 40 x 24 too.

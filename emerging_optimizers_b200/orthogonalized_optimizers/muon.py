@@ -200,8 +200,14 @@ class Muon(OrthogonalizedOptimizer[HookStateT]):
                 use_syrk=self._use_syrk,
             )
             shrink = _SHRINK[self.weight_decay_method](lr, wd) if wd != 0.0 else 0.0
-            scales = [get_muon_scale_factor(p.size(-2), p.size(-1), mode=self._scale_mode) for p in fused]
-            _native.muon_apply_batch([p.data for p in fused], updates, scales, shrink, self._extra_scale_factor, lr)
+            by_device: dict = {}
+            for p, u in zip(fused, updates):
+                by_device.setdefault(p.device, []).append((p, u))
+            for pairs in by_device.values():
+                scales = [get_muon_scale_factor(p.size(-2), p.size(-1), mode=self._scale_mode) for p, _ in pairs]
+                _native.muon_apply_batch(
+                    [p.data for p, _ in pairs], [u for _, u in pairs], scales, shrink, self._extra_scale_factor, lr
+                )
         return None
 
     num_ns_steps = _read_only("num_ns_steps")
