@@ -465,7 +465,8 @@ def run_muon_step(args) -> None:
             params.append(p)
     opt = LayerParallelMuon(params, lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True,
                             weight_decay_method="decoupled", num_ns_steps=5, scale_mode="shape_scaling",
-                            coefficient_type="simple", fp32_matmul_prec="medium", use_syrk=True)  # fmt: skip
+                            coefficient_type="simple", fp32_matmul_prec="medium", use_syrk=True,
+                            **({"bucket_numel": args.bucket_numel} if args.bucket_numel else {}))  # fmt: skip
 
     def barrier() -> None:
         if world > 1:
@@ -600,6 +601,8 @@ def main() -> None:
     ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step", "tp_ns"],
                     help="newton_schulz (default, the headline metric) or muon_step (BASELINE config 3)")
     ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
+    ap.add_argument("--bucket-numel", type=int, default=0,
+                    help="muon_step: elements per rank and exchange bucket (0: the optimizer's default)")
     args = ap.parse_args()
     if args.shape is not None:
         global M, N_COLS

@@ -29,6 +29,7 @@ _STATUS_NAMES = {
 _PROTOTYPES: dict[str, tuple] = {
     "eo_version": (c_char_p, []),
     "eo_last_error": (c_char_p, []),
+    "eo_set_option": (c_int, [c_char_p, c_int]),
     "eo_read_device_status": (c_int, [POINTER(c_uint32), c_void_p]),
     "eo_gemm": (
         c_int,
@@ -178,6 +179,11 @@ def require_cuda(t: torch.Tensor, name: str = "tensor") -> None:
             f"{name} is on {t.device}; emerging_optimizers_b200 runs on CUDA sm_100 devices only "
             "(there is no CPU path)."
         )
+
+
+def set_option(name: str, value: int) -> None:
+    """Set a process-wide tuning knob of the library (see ``eo_set_option``), e.g. ``("gemm_tile_m", 256)``."""
+    _check(lib().eo_set_option(name.encode(), int(value)), "eo_set_option")
 
 
 def read_device_status(device: torch.device | None = None) -> int:

@@ -62,6 +62,7 @@ constexpr int kMaxDevices = 64;
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
 
 int device_setup(DeviceInfo** out) {
   int dev = 0;
@@ -79,7 +80,9 @@ int device_setup(DeviceInfo** out) {
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_device_status));
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.noalloc_partials), g_noalloc_partials));
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.sched_ptr), g_sched_words));
-    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kGemmSmemBytes));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
     EO_CUDA(cudaFuncSetAttribute(eo::eo_ns_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kSmallSmemBytes));
@@ -237,20 +240,36 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
           ((strideC * c_eb) % 16 == 0);
   p.vec_ok = vec ? 1 : 0;
 
+  // Tile height: 256-row tiles (two MMAs per k-step on one B tile) move a third fewer operand bytes per FLOP; they
+  // pay off when every SM still gets several tiles and K is long enough to hide the un-overlapped epilogue.
+  p.bm = 128;
+  p.stages = eo::kStages;
+  {
+    const int want = g_option_gemm_bm;
+    const long long t_wide = (static_cast<long long>((M + 255) / 256) * ((N + 255) / 256)) / (tri ? 2 : 1) * batch;
+    const bool fits = tp == nullptr && precision == 0 && M >= 256 && N >= 256;
+    const bool good = K >= 1024 && 4 * t_wide >= 3LL * dev->sm_count;
+    if (fits && (want == 256 || (want == 0 && good))) {
+      p.bm = 256;
+      p.stages = 3;
+    }
+  }
   // Tile width: 256 unless the problem is narrow or the wider tile leaves SMs idle.
-  p.tiles_m = (M + eo::kBlockM - 1) / eo::kBlockM;
+  p.tiles_m = (M + p.bm - 1) / p.bm;
   auto count_tiles = [&](int bn, int* tiles_n) {
     *tiles_n = (N + bn - 1) / bn;
     if (!tri) return p.tiles_m * (*tiles_n);
     int total = 0;
-    const int ratio = bn / eo::kBlockM;
-    for (int j = 0; j < *tiles_n; ++j) total += p.tiles_m - j * ratio;
+    for (int j = 0; j < *tiles_n; ++j) {
+      const int first = (j * bn) / p.bm;
+      if (first < p.tiles_m) total += p.tiles_m - first;
+    }
     return total;
   };
   int tn256 = 0, tn128 = 0;
   const long long t256 = static_cast<long long>(count_tiles(256, &tn256)) * batch;
   const long long t128 = static_cast<long long>(count_tiles(128, &tn128)) * batch;
-  bool narrow = (N <= 128) || (t256 < dev->sm_count && t128 > t256);
+  bool narrow = p.bm == 128 && ((N <= 128) || (t256 < dev->sm_count && t128 > t256));
   if (tp != nullptr) {
     narrow = tp_tile_n(N) == 128;
     p.tp_world = tp->world;
@@ -276,7 +295,10 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     dev->sched_next++;
   }
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-  eo::eo_gemm_kernel<<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  if (p.bm == 256)
+    eo::eo_gemm_kernel<2><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  else
+    eo::eo_gemm_kernel<1><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }
@@ -288,6 +310,16 @@ extern "C" {
 const char* eo_version(void) { return "eo_b200 0.1.0 sm_100a"; }
 
 const char* eo_last_error(void) { return g_err; }
+
+int eo_set_option(const char* name, int value) {
+  if (name == nullptr) return fail(EO_ERR_BAD_ARG, "option name is NULL");
+  if (strcmp(name, "gemm_tile_m") == 0) {
+    if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
+    g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  return fail(EO_ERR_BAD_ARG, "unknown option %s", name);
+}
 
 int eo_read_device_status(uint32_t* host_code, void* stream) {
   if (host_code == nullptr) return fail(EO_ERR_BAD_ARG, "host_code is NULL");

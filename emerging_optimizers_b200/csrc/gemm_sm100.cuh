@@ -28,7 +28,7 @@ constexpr int kMaxBlockN = 256;
 constexpr int kRowBytes = 128;  // one swizzle row: 64 bf16 along the contiguous dimension
 constexpr int kBlockK = 64;     // K extent of one pipeline stage
 constexpr int kMaxPlanes = 3;   // bf16 planes of a split-fp32 operand
-constexpr int kStages = 4;
+constexpr int kStages = 4;       // ring depth with 128-row A tiles (48 KiB stages); 3 with 256-row A tiles (64 KiB)
 constexpr int kStageABytes = kBlockM * kRowBytes;     // 16 KiB
 constexpr int kStageBBytes = kMaxBlockN * kRowBytes;  // 32 KiB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;
@@ -48,6 +48,9 @@ constexpr int kGemmSmemBytes = kStages * kStageBytes + 512 + 1024;
 struct GemmParams {
   int batch, M, N, K;
   int bn;          // tile width: 128 or 256
+  int bm;          // tile height: 128, or 256 = two 128-row MMAs per k-step sharing one B tile (one accumulator
+                   // each, so the whole of TMEM belongs to one tile): a third fewer operand bytes per FLOP
+  int stages;      // ring depth: 4 (bm 128) or 3 (bm 256)
   int a_mn, b_mn;  // operand stored MN-major (1) or K-major (0)
   int nterms;      // operand-plane pairs accumulated into one result (1: plain bf16; 6: split-fp32 product)
   int term_a[6];   // plane of A used by term t
@@ -84,15 +87,15 @@ struct GemmParams {
   unsigned int* tp_flags[8];    // per owner: flag words of this rank, [slot]
 };
 
-__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
+                                            const int bm = kBlockM) {
   b = t / p.tiles_per_batch;
   int r = t - b * p.tiles_per_batch;
   if (p.tri) {
-    const int ratio = p.bn / kBlockM;
     tj = 0;
     ti = 0;
     for (int j = 0; j < p.tiles_n; ++j) {
-      const int first = j * ratio;
+      const int first = (j * p.bn) / bm;  // first row block that reaches column block j (bm is a constant here)
       const int cnt = p.tiles_m - first;
       if (r < cnt) {
         tj = j;
@@ -253,12 +256,15 @@ __device__ __forceinline__ void push_chunk(const GemmParams& p, const uint32_t (
   }
 }
 
+// kHalves = 1: 128-row tiles, four 48 KiB stages, two alternating accumulators.
+// kHalves = 2: 256-row tiles (two MMAs per k-step on one B tile), three 64 KiB stages, one accumulator per half.
+template <int kHalves>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     eo_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the ring so that descriptor arithmetic holds.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);  // 4 x 48 KiB = 3 x 64 KiB
   uint64_t* full_bar = bars;                     // [kStages]
   uint64_t* empty_bar = bars + kStages;          // [kStages]
   uint64_t* acc_full_bar = bars + 2 * kStages;   // [2]
@@ -279,7 +285,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full_bar[s], 1);
-      mbar_init(&acc_empty_bar[s], kEpilogueWarps);
+      // bm 128: all epilogue warps drain one accumulator; bm 256: half of them drain each of the two
+      mbar_init(&acc_empty_bar[s], kHalves == 2 ? kEpilogueWarps / 2 : kEpilogueWarps);
     }
     for (int s = 0; s < kTileQueue; ++s) {
       mbar_init(&tq_full_bar[s], 1);
@@ -305,7 +312,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   constexpr int bk = kBlockK;
   const int num_kb = (p.K + bk - 1) / bk;
   const int num_it = num_kb * p.nterms;  // pipeline iterations per tile
-  const uint32_t stage_tx = static_cast<uint32_t>(kStageABytes + p.bn * kRowBytes);
+  constexpr int halves = kHalves;                       // MMAs (and accumulators) per k-step and tile
+  constexpr int bm = kHalves * kBlockM;                 // tile height
+  constexpr int a_bytes = bm * kRowBytes;               // A part of a stage: 16 or 32 KiB
+  constexpr int stage_bytes = a_bytes + kStageBBytes;   // 48 or 64 KiB
+  constexpr int stages = (kHalves == 2) ? 3 : kStages;  // 192 KiB of ring either way
+  const uint32_t stage_tx = static_cast<uint32_t>(a_bytes + p.bn * kRowBytes);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -331,11 +343,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         if (t < 0) break;
         int b, ti, tj;
-        decode_tile(p, t, b, ti, tj);
-        const int m0 = ti * kBlockM;
+        decode_tile(p, t, b, ti, tj, bm);
+        const int m0 = ti * bm;
         const int n0 = tj * p.bn;
-        // SYRK tile on the diagonal: its 128 rows are among the rows of the B tile, which then serves both operands.
-        const bool a_in_b = p.same_ab && m0 >= n0 && m0 + kBlockM <= n0 + p.bn;
+        // SYRK tile on the diagonal: its rows are among the rows of the B tile, which then serves both operands.
+        const bool a_in_b = p.same_ab && m0 >= n0 && m0 + bm <= n0 + p.bn;
         const uint32_t tx = a_in_b ? static_cast<uint32_t>(p.bn * kRowBytes) : stage_tx;
         int term = 0, kb = 0;
         for (int it = 0; it < num_it; ++it) {
@@ -346,17 +358,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ok = false;
             break;
           }
-          uint8_t* sa = smem + stage * kStageBytes;
-          uint8_t* sb = sa + kStageABytes;
+          uint8_t* sa = smem + stage * stage_bytes;
+          uint8_t* sb = sa + a_bytes;
           mbar_expect_tx(&full_bar[stage], tx);
           const int k0 = kb * bk;
           if (a_in_b) {
             // nothing to load for A
           } else if (!p.a_mn) {
-            tma_load_3d(sa, tmA, &full_bar[stage], k0, m0, b);  // box {bk, 128, 1}
+            for (int q = 0; q < halves; ++q)  // box {bk, 128, 1}
+              tma_load_3d(sa + q * kStageABytes, tmA, &full_bar[stage], k0, m0 + q * kBlockM, b);
           } else {
             // box {bk (M), bk (K), 1}: one 128-byte-wide M atom per copy
-            for (int q = 0; q < kBlockM / bk; ++q)
+            for (int q = 0; q < bm / bk; ++q)
               tma_load_3d(sa + q * bk * kRowBytes, tmA, &full_bar[stage], m0 + q * bk, k0, b);
           }
           if (!p.b_mn) {
@@ -366,7 +379,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             for (int q = 0; q < p.bn / bk; ++q)
               tma_load_3d(sb + q * bk * kRowBytes, tmB, &full_bar[stage], n0 + q * bk, k0, b);
           }
-          if (++stage == kStages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -400,19 +413,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tq_phase ^= 1u;
         }
         if (t < 0) break;
-        if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
+        // Accumulators: bm 128 alternates between the two; bm 256 needs both (rows 0-127 and 128-255 of the tile).
+        bool acc_ok = true;
+#pragma unroll
+        for (int h = 0; h < halves; ++h)
+          acc_ok = acc_ok && mbar_wait(&acc_empty_bar[halves == 2 ? h : ab], aphase ^ 1u);
+        if (!acc_ok) {
           report(p, kStatusTimeoutMma);
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>((halves == 2 ? 0 : ab) * kMaxBlockN);
         // Offset of the A operand inside the stage: its own slot, or its rows inside the B tile (see the producer).
         uint32_t a_off = 0;
         if (p.same_ab) {
           int b, ti, tj;
-          decode_tile(p, t, b, ti, tj);
-          const int m0 = ti * kBlockM, n0 = tj * p.bn;
-          if (m0 >= n0 && m0 + kBlockM <= n0 + p.bn) a_off = static_cast<uint32_t>(kStageABytes + (m0 - n0) * kRowBytes);
+          decode_tile(p, t, b, ti, tj, bm);
+          const int m0 = ti * bm, n0 = tj * p.bn;
+          if (m0 >= n0 && m0 + bm <= n0 + p.bn) a_off = static_cast<uint32_t>(a_bytes + (m0 - n0) * kRowBytes);
         }
         for (int it = 0; it < num_it; ++it) {
           if (!mbar_wait(&full_bar[stage], phase)) {
@@ -421,34 +439,48 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-          const uint32_t sb = sa + kStageABytes;
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          const uint32_t sb = sa + static_cast<uint32_t>(a_bytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const uint64_t da = make_smem_desc(sa + a_off + k * p.adv_a, p.lbo_a, p.sbo_a);
             const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
-            umma_f16(tmem_d, da, db, idesc, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < halves; ++h) {
+              // rows 128 h .. 128 h + 127 of the A tile start 16 KiB further on, in either operand layout
+              const uint64_t da = make_smem_desc(sa + a_off + h * kStageABytes + k * p.adv_a, p.lbo_a, p.sbo_a);
+              umma_f16(tmem_d + static_cast<uint32_t>(h * kMaxBlockN), da, db, idesc, (it | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&empty_bar[stage]);
-          if (++stage == kStages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(&acc_full_bar[ab]);
-        if (++ab == 2) {
-          ab = 0;
+        if (halves == 2) {
+          umma_commit(&acc_full_bar[0]);
+          umma_commit(&acc_full_bar[1]);
           aphase ^= 1u;
+        } else {
+          umma_commit(&acc_full_bar[ab]);
+          if (++ab == 2) {
+            ab = 0;
+            aphase ^= 1u;
+          }
         }
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
-    const int chunk0 = (warp - 2) >> 2;    // this warp takes chunks chunk0, chunk0 + 2, ...
-    constexpr int kChunkStep = kEpilogueWarps / 4;
-    int ab = 0;
+    const int group = (warp - 2) >> 2;     // first or second set of four warps
+    // bm 128: both sets work on the same accumulator and alternate 32-column chunks.
+    // bm 256: the first set drains rows 0-127 (accumulator 0), the second rows 128-255 (accumulator 1).
+    constexpr bool wide_m = (halves == 2);
+    const int chunk0 = wide_m ? 0 : group;
+    constexpr int kChunkStep = wide_m ? 1 : kEpilogueWarps / 4;
+    int ab = wide_m ? group : 0;
     uint32_t aphase = 0;
     int tq = 0;
     uint32_t tq_phase = 0;
@@ -466,8 +498,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       }
       if (t < 0) break;
       int b, ti, tj;
-      decode_tile(p, t, b, ti, tj);
-      const int m0 = ti * kBlockM;
+      decode_tile(p, t, b, ti, tj, bm);
+      const int m0 = ti * bm + (wide_m ? group * kBlockM : 0);  // first row this set of warps is responsible for
       const int n0 = tj * p.bn;
       if (!mbar_wait(&acc_full_bar[ab], aphase)) {
         report(p, kStatusTimeoutEpilogue);
@@ -520,7 +552,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[ab]);
-      if (++ab == 2) {
+      if (wide_m) {
+        aphase ^= 1u;  // the same accumulator again for the next tile
+      } else if (++ab == 2) {
         ab = 0;
         aphase ^= 1u;
       }

@@ -41,6 +41,13 @@ const char* eo_version(void);
 const char* eo_last_error(void);
 
 /*
+ * Tuning knobs (process-wide).  "gemm_tile_m": 0 (default) lets each launch choose between 128-row tiles and
+ * 256-row tiles (two MMAs per k-step sharing one B tile: fewer operand bytes per FLOP, used for large problems
+ * with long K); 128 or 256 forces one.  Results do not depend on the choice.
+ */
+int eo_set_option(const char* name, int value);
+
+/*
  * Reads and clears the status word that kernels of this library write when one of their bounded
  * waits (mbarrier, accumulator hand-off, peer flag) runs out.  Synchronises `stream` first.
  * *host_code receives 0 when every kernel completed normally.

@@ -107,6 +107,33 @@ def test_gemm_all_operand_layouts_bit_exact(a_mn, b_mn, m, n, k, batch):
     assert torch.equal(out32, ref.float() * 3.0)
 
 
+@pytest.mark.parametrize("tile_m", [128, 256])
+def test_both_tile_heights_bit_exact(tile_m):
+    """The launcher picks 128- or 256-row tiles per problem; both must give the same bits on every layout."""
+    nat.set_option("gemm_tile_m", tile_m)
+    try:
+        for n, k, trans in ((256, 64, False), (1000, 136, False), (2048, 1024, True), (2304, 192, True)):
+            a = int_tensor(n, k, seed=n) if not trans else int_tensor(k, n, seed=n).T
+            c = int_tensor(n, n, seed=1)
+            c = (c + c.T).contiguous()
+            assert torch.equal(tk.tsyrk_ex(a, c, alpha=0.5, beta=0.25), _exact_ref(a, c, 0.5, 0.25))
+        for m, n, k, a_mn, b_mn, batch in ((256, 256, 64, 0, 0, 1), (512, 768, 256, 0, 1, 1), (200, 304, 72, 1, 1, 1),
+                                           (1024, 2048, 520, 1, 0, 1), (256, 512, 1024, 0, 1, 3)):  # fmt: skip
+            lead = (batch,) if batch > 1 else ()
+            a = int_tensor(*lead, m, k, seed=8) if not a_mn else int_tensor(*lead, k, m, seed=8).mT
+            b = int_tensor(*lead, k, n, seed=9) if b_mn else int_tensor(*lead, n, k, seed=9).mT
+            c = int_tensor(*lead, m, n, seed=10)
+            out = torch.empty(*lead, m, n, dtype=torch.bfloat16, device="cuda")
+            nat.gemm(a, b, c, out, alpha=0.5, beta=0.25)
+            assert torch.equal(out, (0.5 * (a.float() @ b.float()) + 0.25 * c.float()).bfloat16())
+        x = (randn_tensor(1024, 4096, seed=14) / 64).bfloat16()
+        first = tk.tsyrk_ex(x)
+        nat.set_option("gemm_tile_m", 128)
+        assert torch.equal(first, tk.tsyrk_ex(x))  # same bits from either tile height
+    finally:
+        nat.set_option("gemm_tile_m", 0)
+
+
 def test_config2_batched_syrk_full_size_properties():
     """BASELINE config 2 shape: 32 x (2048 x 8192), entries N(0, 1/8192) so that diag(A) is about 1."""
     g = torch.Generator(device="cuda").manual_seed(1)
