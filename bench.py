@@ -35,7 +35,7 @@ if ROOT not in sys.path:
 M, N_COLS, NS_STEPS, COEFF = 8192, 28672, 5, "simple"
 CPU_SAMPLE = (2048, 7168)  # corner block timed on the host
 NOMINAL_BF16_TFLOPS = 2250.0
-TRAFFIC_BYTES_PER_LAUNCH = 0.82e9
+TRAFFIC_BYTES_PER_LAUNCH = 0.67e9
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
@@ -407,7 +407,7 @@ def run_gpu_arm(args) -> None:
                 "frac": (achieved / peak) if achieved else None,
                 "frac_of_burst_peak": (achieved / float(peaks["bf16_tflops"])) if achieved else None,
                 # DRAM bytes per launch, from the ncu capture of one iteration on 4096 x 16384 (read + write of the
-                # Gram, A^2 and BX launches: 247 + 35 + 417 MB) scaled by operand bytes to this shape and averaged
+                # Gram, A^2 and BX launches: 138 + 35 + 398 MB) scaled by operand bytes to this shape and averaged
                 # over the three launches; see profiles/ and DESIGN.md.
                 "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
                 "algorithmic_flops_per_launch": sym * 2 / n_launch if n_launch else None,
