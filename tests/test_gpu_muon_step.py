@@ -161,3 +161,39 @@ def test_layer_parallel_two_gpus_equals_single_process_bitwise():
         assert results[r]["status"] == 0
         for i, p in enumerate(ref_params):
             assert torch.equal(results[r]["params"][i], p.detach().cpu()), (r, i)
+
+
+def test_per_head_muon_subclass_pattern():
+    """The reference's recipe for per-head / split-QKV orthogonalization (examples/per-head-muon.ipynb and the
+    docstring at orthogonalized_optimizer.py:68-87 there): a Muon subclass overrides ``orthogonalize``, views the
+    (heads * d, n) gradient as (heads, d, n) and orthogonalizes every head on its own - here one batched call that
+    lands on the fused small-matrix kernel.  It must equal orthogonalizing each head separately."""
+    heads, d, n = 6, 128, 512
+
+    class PerHeadMuon(Muon):
+        def orthogonalize(self, p, grad, **kwargs):
+            out = self.scaled_orthogonalize_fn(grad.view(heads, d, n))
+            return out.reshape(heads * d, n)
+
+    kw = dict(KW, scale_mode="spectral")
+    w = randn_tensor(heads * d, n, seed=70, scale=0.02)
+    g = randn_tensor(heads * d, n, seed=71, scale=1e-3).bfloat16().float()
+    p = torch.nn.Parameter(w.clone())
+    p.grad = g.clone()
+    opt = PerHeadMuon([p], use_syrk=True, **kw)
+    assert not opt._fused_step_applies()  # customised: the per-parameter path is taken
+    opt.step()
+
+    # the same step written out head by head
+    mom = torch.zeros_like(w).lerp_(g, 1 - kw["momentum"])
+    upd = g.lerp(mom, kw["momentum"])
+    want = w.clone()
+    want.add_(want, alpha=-kw["weight_decay"] * kw["lr"])
+    with fp32_matmul_precision("medium"):
+        per_head = torch.cat(
+            [muon_utils.newton_schulz(upd[h * d : (h + 1) * d], 5, "simple", use_syrk=True) for h in range(heads)]
+        )
+    scale = max(d, n) ** 0.5  # "spectral" scale from the size of one head, not of the fused parameter
+    want.add_(per_head * scale * 1.0, alpha=-kw["lr"])
+    assert torch.equal(p.detach(), want)
+    assert nat.read_device_status() == 0
