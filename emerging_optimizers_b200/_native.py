@@ -94,6 +94,7 @@ _PROTOTYPES: dict[str, tuple] = {
         c_int,
         [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_uint32, c_void_p],
     ),
+    "eo_tp_gram_mirror": (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -562,3 +563,10 @@ def tp_gram_allreduce(x: torch.Tensor, world: int, rank: int, inbox_ptrs, flag_p
             ld_gram, seq, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_tp_gram_allreduce")
+
+
+def tp_gram_mirror(gram: torch.Tensor, n: int, ld: int) -> None:
+    """Copy the lower triangle of the local ``n x n`` Gram buffer onto its upper triangle (after the exchange barrier)."""
+    with torch.cuda.device(gram.device), _Timed("tp_mirror", 1, gram.device):
+        rc = lib().eo_tp_gram_mirror(gram.data_ptr(), n, ld, _stream(gram))
+    _check(rc, "eo_tp_gram_mirror")

@@ -247,7 +247,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   {
     const int want = g_option_gemm_bm;
     const long long t_wide = (static_cast<long long>((M + 255) / 256) * ((N + 255) / 256)) / (tri ? 2 : 1) * batch;
-    const bool fits = tp == nullptr && precision == 0 && M >= 256 && N >= 256;
+    const bool fits = precision == 0 && M >= 256 && N >= 256;
     const bool good = K >= 1024 && 4 * t_wide >= 3LL * dev->sm_count;
     if (fits && (want == 256 || (want == 0 && good))) {
       p.bm = 256;
@@ -743,6 +743,7 @@ int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, 
   for (int r = 0; r < world; ++r) q.gram[r] = static_cast<unsigned short*>(gram_ptrs[r]);
   q.ld = ld_gram;
   q.status = dev->status_ptr;
+  q.mirror = 0;  // lower triangle only; eo_tp_gram_mirror completes each rank's copy after the barrier
   const int smem = eo::kBlockM * (q.bn + 8) * 2;
   static bool attr_set[kMaxDevices] = {};
   int devid = 0;
@@ -754,6 +755,17 @@ int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, 
   }
   const int grid = q.slots < 2 * dev->sm_count ? q.slots : 2 * dev->sm_count;
   eo::tp_gram_reduce_kernel<<<grid, eo::kTpReduceThreads, smem, static_cast<cudaStream_t>(stream)>>>(q);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (gram == nullptr || N <= 0 || ld_gram < N) return fail(EO_ERR_BAD_ARG, "bad Gram matrix");
+  const int nb = (N + 31) / 32;
+  eo::mirror_lower_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned short*>(gram), N, ld_gram);
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }

@@ -512,27 +512,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const long long batch_d = static_cast<long long>(b) * p.strideD;
       const int nchunks = p.bn / 32;
       if (p.tp_world > 1) {
-        // Push the whole partial tile to its owner, then let the last of the four warps publish the flag.
-        const int owner = t % p.tp_world;
-        const int slot = t / p.tp_world;
-        unsigned short* tile = p.tp_inbox[owner] + static_cast<long long>(slot) * kBlockM * p.bn;
-        for (int c = chunk0; c < nchunks; c += kChunkStep) {
-          uint32_t acc[32];
-          __syncwarp();
-          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                            static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
-                        acc);
-          tmem_ld_wait();
-          push_chunk(p, acc, tile, quarter * 32 + lane, c * 32);
+        // Push the partial tile to its owner, then let the last warp working on this accumulator publish the flag.
+        // Owners and inbox slots are defined on the 128-row tile grid; a 256-row tile is two of those.
+        int sub = t;
+        bool exists = true;
+        if (wide_m) {
+          const int tm128 = (p.M + kBlockM - 1) / kBlockM;
+          const int ti128 = 2 * ti + group;
+          exists = ti128 < tm128;
+          sub = tj * tm128 - tj * (tj - 1) + (ti128 - 2 * tj);  // index of tile (ti128, tj) among rows >= 2 tj
         }
-        __threadfence_system();
+        const int owner = sub % p.tp_world;
+        const int slot = sub / p.tp_world;
+        unsigned short* tile = p.tp_inbox[owner] + static_cast<long long>(slot) * kBlockM * p.bn;
+        if (exists) {
+          for (int c = chunk0; c < nchunks; c += kChunkStep) {
+            uint32_t acc[32];
+            __syncwarp();
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                              static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
+                          acc);
+            tmem_ld_wait();
+            push_chunk(p, acc, tile, quarter * 32 + lane, c * 32);
+          }
+          __threadfence_system();
+        }
         __syncwarp();
         if (lane == 0) {
-          if (atomicAdd(&push_done[ab], 1u) == static_cast<unsigned int>(kEpilogueWarps - 1)) {
+          constexpr unsigned int kWarpsPerAcc = wide_m ? kEpilogueWarps / 2 : kEpilogueWarps;
+          if (atomicAdd(&push_done[ab], 1u) == kWarpsPerAcc - 1u) {
             push_done[ab] = 0u;
-            __threadfence_system();
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[owner] + slot), "r"(p.tp_seq)
-                         : "memory");
+            if (exists) {
+              __threadfence_system();
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[owner] + slot), "r"(p.tp_seq)
+                           : "memory");
+            }
           }
         }
       } else {

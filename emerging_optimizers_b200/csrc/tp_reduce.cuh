@@ -23,6 +23,8 @@ struct TpReduceParams {
   unsigned short* gram[8];      // per rank: N x ld bf16
   long long ld;
   unsigned int* status;
+  int mirror;  // 1: also store the mirror image of each tile into every rank's matrix; 0: lower triangle only
+               //    (every rank then mirrors its own copy locally, which halves the bytes that cross NVLink)
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(kTpReduceThreads) tp_gram_reduce_kernel(const 
     }
     // Mirrored part: element (row, col) with col < row goes to (col, row); rows of the tile run along memory.
     const int rvec = kBlockM / 8;
-    for (int v = threadIdx.x; v < q.bn * rvec; v += kTpReduceThreads) {
+    for (int v = threadIdx.x; q.mirror && v < q.bn * rvec; v += kTpReduceThreads) {
       const int c = v / rvec, r8 = (v - c * rvec) * 8;
       const int col = n0 + c, row = m0 + r8;
       if (col >= q.N || row >= q.N || col >= row + 7) continue;  // nothing below the diagonal in this group
@@ -133,6 +135,29 @@ __global__ void __launch_bounds__(kTpReduceThreads) tp_gram_reduce_kernel(const 
       }
     }
     __syncthreads();
+  }
+}
+
+// Copy the strict lower triangle of an N x N bf16 matrix onto its upper triangle (32 x 32 blocks through shared
+// memory, coalesced on both sides).  blockIdx.x enumerates the blocks on and below the diagonal.
+__global__ void __launch_bounds__(256) mirror_lower_kernel(unsigned short* __restrict__ a, int N, long long ld) {
+  __shared__ unsigned short tile[32][33];
+  // block (bi, bj), bi >= bj, from the linear index t = bi (bi + 1) / 2 + bj
+  const int t = blockIdx.x;
+  int bi = static_cast<int>((sqrtf(8.0f * static_cast<float>(t) + 1.0f) - 1.0f) * 0.5f);
+  while (bi * (bi + 1) / 2 > t) --bi;
+  while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
+  const int bj = t - bi * (bi + 1) / 2;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    const int row = bi * 32 + r, col = bj * 32 + tx;
+    if (row < N && col < N) tile[r][tx] = a[static_cast<long long>(row) * ld + col];
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    // destination element (bj * 32 + r, bi * 32 + tx) takes source (bi * 32 + tx, bj * 32 + r)
+    const int drow = bj * 32 + r, dcol = bi * 32 + tx;
+    if (drow < N && dcol < N && dcol > drow) a[static_cast<long long>(drow) * ld + dcol] = tile[tx][r];
   }
 }
 

@@ -4,8 +4,9 @@ In ``newton_schulz_tp(..., tp_mode="distributed")`` every rank holds a shard ``X
 dimension and each iteration needs ``A = sum_r X_r X_r^T`` on every rank.  The reference computes the partial
 product and then calls ``all_reduce`` on the full m x m matrix (``muon_utils.py:370-372, 434-436`` there).  Here the
 SYRK kernel's epilogue stores each finished partial tile directly into the memory of the tile's owner rank, the
-owners sum their tiles and store the results (and their mirror images) into every rank's Gram matrix, and one
-group barrier closes the exchange: only lower-triangle tiles travel, in bf16, overlapped with the SYRK main loop.
+owners sum their tiles and store the lower-triangle results into every rank's Gram matrix, one group barrier
+closes the exchange and every rank mirrors its own copy: only lower-triangle data travels, in bf16, overlapped
+with the SYRK main loop.
 
 Buffers live in symmetric memory (``PeerBuffer``) and are cached per (process group, matrix size, device).
 """
@@ -52,6 +53,8 @@ class GramExchange:
                                   self.ld, self.seq)  # fmt: skip
         # Orders every owner's stores before any rank reads its Gram matrix, and this exchange before the next.
         self.gram.barrier()
+        # The owners sent lower triangles only; complete the local copy.
+        _native.tp_gram_mirror(self.gram.local, self.m, self.ld)
         return self.gram.local.view(self.m, self.ld)[:, : self.m]
 
 

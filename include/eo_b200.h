@@ -257,15 +257,17 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
  * stores the bf16 partial straight into the inbox of the tile's owner (rank t mod world) - a plain store to
  * local or peer memory - and publishes `seq` in the owner's flag word.  A second kernel on the owner waits
  * (bounded, about one second; on expiry the device status word is set and the kernel returns) for all
- * `world` partials of each of its tiles, sums them in fp32, rounds to bf16 once and stores the tile and its
- * mirror image into the Gram matrix of every rank.  Only lower-triangle tiles travel: about half the bytes of an
- * all-reduce of the full matrix, and the pushes overlap the main loop of the following tiles.
+ * `world` partials of each of its tiles, sums them in fp32, rounds to bf16 once and stores the lower-triangle part
+ * of the tile into the Gram matrix of every rank.  Only lower-triangle data travels: about half the bytes of an
+ * all-reduce of the full matrix, and the pushes overlap the main loop of the following tiles.  After the barrier
+ * that closes the exchange every rank completes its own copy with eo_tp_gram_mirror (lower -> upper triangle).
  *
  * inbox_ptrs / flag_ptrs / gram_ptrs: host arrays of `world` device pointers, entry r addressing rank r's
  * buffer (peer-mapped, e.g. symmetric memory): inbox of eo_tp_gram_inbox_bytes(N, world) bytes, flags of
  * eo_tp_gram_flag_count(N, world) uint32 (zeroed once at creation), Gram matrix N x ld_gram bf16.
- * `seq` must increase by one with every call on the same buffers (first call: 1).  After the call, and
- * after a barrier across the ranks that orders the owners' stores, every rank's Gram matrix holds the sum.
+ * `seq` must increase by one with every call on the same buffers (first call: 1).  After the call, a
+ * barrier across the ranks that orders the owners' stores, and eo_tp_gram_mirror on the local matrix, every
+ * rank's Gram matrix holds the full symmetric sum.
  * The caller must also order the next call after all ranks have consumed their Gram matrix (the same barrier
  * does both when each rank uses the matrix before its next call).
  *
@@ -277,6 +279,7 @@ size_t eo_tp_gram_flag_count(int N, int world);
 int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, int world, int rank,
                          void* const* inbox_ptrs, void* const* flag_ptrs, void* const* gram_ptrs, int64_t ld_gram,
                          uint32_t seq, void* stream);
+int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream);
 
 #ifdef __cplusplus
 }

@@ -42,7 +42,9 @@ def _worker(rank, world, port, out):
 
     res = {}
     # 1. the exchange alone, integer-valued shards: every partial and the sum are exact in bf16
-    for m, k in ((128, 64), (200, 64), (1000, 64), (512, 128)):
+    for m, k, tile_m in ((128, 64, 0), (200, 64, 0), (1000, 64, 0), (512, 128, 0), (1000, 64, 256), (512, 128, 256),
+                         (264, 64, 256)):  # fmt: skip
+        nat.set_option("gemm_tile_m", tile_m)  # 256: the pushing kernel runs with 256-row tiles (two inbox tiles each)
         g = torch.Generator(device="cpu").manual_seed(100 + m)
         full = torch.randint(-1, 2, (m, world * k), generator=g).to(torch.bfloat16)
         for trans in (False, True):
@@ -52,7 +54,8 @@ def _worker(rank, world, port, out):
             for rep in range(2):  # second call reuses inbox, flags and Gram buffer with the next sequence number
                 a = tp.fused_gram(shard, group).clone()
             want = (full.float() @ full.float().T).to(dev)
-            res[f"gram.{m}.{int(trans)}"] = bool(torch.equal(a.float(), want)) and bool(torch.equal(a, a.T))
+            res[f"gram.{m}.{int(trans)}.{tile_m}"] = bool(torch.equal(a.float(), want)) and bool(torch.equal(a, a.T))
+    nat.set_option("gemm_tile_m", 0)
     # 2. full tensor-parallel Newton-Schulz, both partition dims, fused exchange vs NCCL vs single device
     for shape, pdim in (((512, 2048), 1), ((2048, 512), 0), ((256, 1024), 1)):
         x = _randn(*shape, seed=7)
