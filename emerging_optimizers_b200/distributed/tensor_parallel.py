@@ -59,9 +59,10 @@ class GramExchange:
 
 
 # Largest group for which the fused exchange is chosen by default.  Measured on 8192 x 28672 (five steps, B200,
-# NVSwitch): fused 16.4 / 10.1 / 8.2 ms on 2 / 4 / 8 ranks against 16.3 / 10.3 / 7.4 ms with NCCL's all-reduce; on 8
-# ranks the owners' point-to-point broadcast of the reduced tiles loses to the in-switch reduction NCCL uses.
-FUSED_MAX_WORLD = 4
+# NVSwitch): fused 15.7 / 10.6 / 8.4 ms on 2 / 4 / 8 ranks against 15.5 / 10.0 / 7.6 ms with NCCL's all-reduce: on
+# par for a pair of GPUs, while on larger groups the owners' point-to-point broadcast of the reduced tiles loses to
+# the in-switch reduction NCCL uses.
+FUSED_MAX_WORLD = 2
 
 
 def fused_gram_available(x: torch.Tensor, group: "dist.ProcessGroup | None") -> bool:

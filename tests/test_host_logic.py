@@ -275,4 +275,4 @@ def test_tp_exchange_is_chosen_by_group_size(monkeypatch):
     x = torch.zeros(8, 8, dtype=torch.bfloat16)
     assert not tp.fused_gram_available(x, None)
     assert not tp.fused_gram_available(x, object())  # CPU tensor: never
-    assert tp.FUSED_MAX_WORLD == 4
+    assert tp.FUSED_MAX_WORLD == 2
