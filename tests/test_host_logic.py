@@ -276,3 +276,41 @@ def test_tp_exchange_is_chosen_by_group_size(monkeypatch):
     assert not tp.fused_gram_available(x, None)
     assert not tp.fused_gram_available(x, object())  # CPU tensor: never
     assert tp.FUSED_MAX_WORLD == 2
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    """No fallback: if the shared library is not there, the first use raises and says how to build it."""
+    from emerging_optimizers_b200 import _native
+
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setenv("EO_B200_LIB", str(tmp_path / "libeo_b200.so"))
+    with pytest.raises(_native.NativeLibraryError, match="no CPU or PyTorch fallback"):
+        _native.lib()
+    monkeypatch.delenv("EO_B200_LIB")
+    monkeypatch.setattr(_native, "_lib", None)
+    assert _native.lib().eo_version().decode().startswith("eo_b200")
+
+
+def test_matrix_layout_detection():
+    from emerging_optimizers_b200 import _native
+
+    x = torch.zeros(6, 10)
+    assert _native._mat_layout(x) == (0, 10, 0)
+    assert _native._mat_layout(x.T) == (1, 10, 0)
+    assert _native._mat_layout(x[:, :8]) == (0, 10, 0)  # padded rows
+    b = torch.zeros(3, 6, 10)
+    assert _native._mat_layout(b) == (0, 10, 60)
+    assert _native._mat_layout(b.mT) == (1, 10, 60)
+    assert not _native.is_matrix_layout(torch.zeros(6, 20)[:, ::2])
+    assert _native.is_matrix_layout(torch.zeros(1, 7)) and _native.is_matrix_layout(torch.zeros(7, 1))
+
+
+def test_padded_buffers_keep_rows_tma_addressable():
+    m = muon_utils._empty_matrix((13, 21), torch.bfloat16, torch.device("cpu"))
+    assert tuple(m.shape) == (13, 21) and m.stride(-1) == 1 and m.stride(-2) % 8 == 0
+    b = muon_utils._empty_matrix((3, 13, 21), torch.bfloat16, torch.device("cpu"))
+    assert tuple(b.shape) == (3, 13, 21) and b.stride(-2) % 8 == 0 and b.stride(0) % 8 == 0
+    c = muon_utils._empty_matrix((16, 24), torch.bfloat16, torch.device("cpu"))
+    assert c.is_contiguous()
+    f = muon_utils._empty_matrix((5, 6), torch.float32, torch.device("cpu"))
+    assert f.stride(-2) % 4 == 0
