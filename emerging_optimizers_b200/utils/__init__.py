@@ -1,10 +1,11 @@
 """Precision switch and process-group helpers used by the orthogonalization path.
 
-Mirrors ``emerging_optimizers/utils/__init__.py:25-54`` of the reference (names and behaviour).
+Same public names and behaviour as ``emerging_optimizers/utils/__init__.py:25-54`` of the reference.
 """
 
-from contextlib import contextmanager
-from typing import Generator, Literal
+from __future__ import annotations
+
+from typing import Literal
 
 import torch
 
@@ -14,30 +15,41 @@ __all__ = ["fp32_matmul_precision", "FP32MatmulPrecT", "get_pg_size", "get_pg_ra
 FP32MatmulPrecT = Literal["highest", "high", "medium"]
 
 
-@contextmanager
-def fp32_matmul_precision(precision: FP32MatmulPrecT = "highest") -> Generator[None, None, None]:
-    """Set ``torch.set_float32_matmul_precision`` inside the block and put the old value back after it.
+class fp32_matmul_precision:  # noqa: N801 - used as ``with fp32_matmul_precision("medium"):``
+    """Switch ``torch.set_float32_matmul_precision`` for the duration of a ``with`` block.
 
-    The Newton-Schulz driver reads this ambient setting to choose between the bf16 kernels ("medium") and the
-    fp32-accurate ones, exactly as the reference does (``muon_utils.py:245``).
+    The Newton-Schulz driver reads this ambient setting to choose its arithmetic, exactly as the reference does
+    (``muon_utils.py:245`` there): "medium" selects the bf16 tensor-core kernels, "high" / "highest" the
+    fp32-accurate split-bf16 products.  The previous value comes back on exit, also when the block raises.
     """
-    saved = torch.get_float32_matmul_precision()
-    torch.set_float32_matmul_precision(precision)
-    try:
-        yield
-    finally:
-        torch.set_float32_matmul_precision(saved)
+
+    def __init__(self, precision: FP32MatmulPrecT = "highest") -> None:
+        self.precision = precision
+        self._outer: str | None = None
+
+    def __enter__(self) -> None:
+        self._outer = torch.get_float32_matmul_precision()
+        torch.set_float32_matmul_precision(self.precision)
+
+    def __exit__(self, exc_type, exc, tb) -> bool:
+        torch.set_float32_matmul_precision(self._outer)
+        return False
+
+
+def _group_or_none(group: "torch.distributed.ProcessGroup | None"):
+    """``group`` if it can be queried (torch.distributed initialised and a group given), else ``None``."""
+    if group is not None and torch.distributed.is_available() and torch.distributed.is_initialized():
+        return group
+    return None
 
 
 def get_pg_size(group: "torch.distributed.ProcessGroup | None" = None) -> int:
-    """World size of ``group``; 1 when torch.distributed is not initialised or no group is given."""
-    if group is None or not torch.distributed.is_initialized():
-        return 1
-    return group.size()
+    """Number of ranks in ``group``; 1 for a single process."""
+    g = _group_or_none(group)
+    return 1 if g is None else g.size()
 
 
 def get_pg_rank(group: "torch.distributed.ProcessGroup | None" = None) -> int:
-    """Rank inside ``group``; 0 when torch.distributed is not initialised or no group is given."""
-    if group is None or not torch.distributed.is_initialized():
-        return 0
-    return group.rank()
+    """This process's rank in ``group``; 0 for a single process."""
+    g = _group_or_none(group)
+    return 0 if g is None else g.rank()
