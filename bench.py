@@ -539,6 +539,8 @@ def run_tp_ns(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     os.environ["EO_TP_GRAM"] = "nccl" if args.exchange == "nccl" else "fused"
+    if args.tp_shard_poly_min_world:
+        muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD = args.tp_shard_poly_min_world
     cols = N_COLS // world
     g = torch.Generator(device=dev).manual_seed(3 + rank)
     x = torch.randn(M, cols, generator=g, device=dev)
@@ -601,6 +603,8 @@ def main() -> None:
     ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step", "tp_ns"],
                     help="newton_schulz (default, the headline metric) or muon_step (BASELINE config 3)")
     ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
+    ap.add_argument("--tp-shard-poly-min-world", type=int, default=0,
+                    help="tp_ns: smallest group that computes S = bA + cA^2 in row blocks per rank (0: library default)")
     ap.add_argument("--bucket-numel", type=int, default=0,
                     help="muon_step: elements per rank and exchange bucket (0: the optimizer's default)")
     args = ap.parse_args()

@@ -70,6 +70,18 @@ def _worker(rank, world, port, out):
             y_full = muon_utils.newton_schulz(x.to(dev), 5, "quintic", use_syrk=True)
         ref = y_full.chunk(world, dim=pdim)[rank]
         res[f"ns.{shape}.{pdim}"] = (_rel(y_fused, ref), _rel(y_nccl, ref), tuple(y_fused.shape) == tuple(shard.shape))
+    # 3. S = b A + c A^2 computed in row blocks per rank and all-gathered: same bits as the redundant computation
+    x = _randn(512, 2048, seed=9)
+    shard = x.chunk(world, dim=1)[rank].contiguous().to(dev)
+    with fp32_matmul_precision("medium"):
+        y_plain = muon_utils.newton_schulz_tp(shard, 5, "quintic", group, partition_dim=1, tp_mode="distributed", use_syrk=True)
+        saved = muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD
+        muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD = 2
+        try:
+            y_sharded = muon_utils.newton_schulz_tp(shard, 5, "quintic", group, partition_dim=1, tp_mode="distributed", use_syrk=True)
+        finally:
+            muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD = saved
+    res["sharded_poly"] = bool(torch.equal(y_plain, y_sharded))
     torch.cuda.synchronize()
     res["status"] = nat.read_device_status(dev)
     out[rank] = res
@@ -88,6 +100,8 @@ def test_fused_gram_exchange_and_tp_newton_schulz_two_gpus():
         assert res["status"] == 0
         for key, val in res.items():
             if key.startswith("gram."):
+                assert val, (rank, key)
+            elif key == "sharded_poly":
                 assert val, (rank, key)
             elif key.startswith("ns."):
                 err_fused, err_nccl, shape_ok = val
