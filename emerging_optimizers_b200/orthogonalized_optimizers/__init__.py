@@ -1,5 +1,11 @@
-"""Orthogonalized optimizers on the sm_100a Newton-Schulz kernels: ``OrthogonalizedOptimizer``, ``Muon`` and the
-``muon_utils`` driver functions."""
+"""Orthogonalized optimizers on the sm_100a Newton-Schulz kernels: the ``OrthogonalizedOptimizer`` base, ``Muon``
+and the optimizers derived from them (``AdaptiveMuon``, ``MuonHyperball``, ``PolarGrad``, ``Scion``, ``Spel``),
+plus the ``muon_utils`` driver functions and ``spectral_clipping_utils``."""
 
+from emerging_optimizers_b200.orthogonalized_optimizers.adaptive_muon import *  # noqa: F401,F403
 from emerging_optimizers_b200.orthogonalized_optimizers.muon import *  # noqa: F401,F403
+from emerging_optimizers_b200.orthogonalized_optimizers.muon_hyperball import *  # noqa: F401,F403
 from emerging_optimizers_b200.orthogonalized_optimizers.orthogonalized_optimizer import *  # noqa: F401,F403
+from emerging_optimizers_b200.orthogonalized_optimizers.polargrad import *  # noqa: F401,F403
+from emerging_optimizers_b200.orthogonalized_optimizers.scion import *  # noqa: F401,F403
+from emerging_optimizers_b200.orthogonalized_optimizers.spel import *  # noqa: F401,F403

@@ -1,0 +1,66 @@
+"""Shared by the CPU and GPU tests of the optimizers built on Newton-Schulz: rebuild a golden case (weights and
+gradients from their seeds), run it on a device, and hand back what the golden file recorded."""
+
+import json
+import os
+
+import numpy as np
+import torch
+
+import emerging_optimizers_b200.orthogonalized_optimizers as opt_pkg
+import emerging_optimizers_b200.weight_update_hooks as hooks_pkg
+
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+with open(os.path.join(GOLDEN, "consumer_cases.json")) as f:
+    CASES = json.load(f)
+SHAPES = [tuple(s) for s in CASES["shapes"]]
+STEPS = CASES["steps"]
+OPTIMIZER_CASES = sorted(CASES["optimizers"])
+
+
+def golden():
+    return np.load(os.path.join(GOLDEN, "consumers.npz"))
+
+
+def randn(*shape, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32) * scale
+
+
+def initial_weights(cls, kw):
+    ws = []
+    for i, s in enumerate(SHAPES):
+        w = randn(*s, seed=400 + i, scale=0.05)
+        if cls == "MuonHyperball":
+            w = w * (kw["hyperball_radius"] / w.norm())
+        ws.append(w)
+    return ws
+
+
+def run_case(name, precision, device):
+    """Run the recorded steps; returns {"p<i>.after<step>" | "p<i>.<state key>": cpu tensor} and the initial
+    weights."""
+    cls, kw, hook = CASES["optimizers"][name]
+    init = initial_weights(cls, kw)
+    params = [torch.nn.Parameter(w.clone().to(device)) for w in init]
+    extra = {} if hook is None else {"weight_update_hook": getattr(hooks_pkg, hook[0])(**hook[1])}
+    opt = getattr(opt_pkg, cls)(params, fp32_matmul_prec=precision, **kw, **extra)
+    got = {}
+    for step in range(STEPS):
+        for i, p in enumerate(params):
+            p.grad = randn(*p.shape, seed=450 + 10 * step + i, scale=1e-2).to(device)
+        opt.step()
+        if step in (0, STEPS - 1):
+            for i, p in enumerate(params):
+                got[f"p{i}.after{step}"] = p.detach().cpu().clone()
+    for i, p in enumerate(params):
+        for key, t in opt.state[p].items():
+            got[f"p{i}.{key}"] = t.detach().cpu().clone()
+    return got, init
+
+
+def rel_fro(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-300))

@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the reference implementation on CPU.
 
-Run once, in a container that has the reference checkout (read-only) at $EO_REFERENCE (default /root/reference):
+Run once, in a container that has the reference checkout (read-only) at the path given by $EO_REFERENCE:
 
-    python tests/golden/make_golden.py
+    EO_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
 The reference is imported, never copied.  The outputs (small .npz / .json files next to this script) are
 committed; the tests read only those files, so they also run where the reference checkout is absent.
@@ -20,7 +20,9 @@ import torch.multiprocessing as mp
 
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("EO_REFERENCE", "/root/reference")
+REF = os.environ.get("EO_REFERENCE")
+if not REF:
+    raise SystemExit("set EO_REFERENCE to the root of the reference checkout")
 sys.path.insert(0, REF)
 
 from emerging_optimizers.orthogonalized_optimizers import muon_utils as ref_mu  # noqa: E402
@@ -173,12 +175,125 @@ def make_tp() -> None:
     np.savez_compressed(os.path.join(HERE, "ns_tp.npz"), **out)
 
 
+CONSUMER_SHAPES = [(32, 48), (48, 32)]
+CONSUMER_STEPS = 3
+# name: (optimizer class, constructor kwargs, weight-update hook (class name, kwargs) or None)
+CONSUMER_CASES = {
+    "scion": ("Scion", dict(lr=0.05, momentum=0.9, num_ns_steps=5, spectral_radius=1.5), None),
+    "spel": ("Spel", dict(lr=0.05, momentum=0.9, weight_decay=0.1, nesterov=True, num_ns_steps=5), None),
+    "polargrad": (
+        "PolarGrad",
+        dict(lr=0.05, momentum=0.9, weight_decay=0.01, extra_scale_factor=0.5, coefficient_type="polar_express",
+             num_ns_steps=6),
+        None,
+    ),
+    "adamuon": (
+        "AdaptiveMuon",
+        dict(lr=0.02, momentum=0.9, weight_decay=0.05, nesterov=True, moment2_method="adamuon"),
+        None,
+    ),
+    "normuon": (
+        "AdaptiveMuon",
+        dict(lr=0.02, momentum=0.9, weight_decay=0.05, moment2_method="normuon", scale_mode="shape_scaling"),
+        None,
+    ),
+    "namo": (
+        "AdaptiveMuon",
+        dict(lr=0.02, momentum=0.9, weight_decay=0.05, nesterov=True, moment2_method="namo", extra_scale_factor=0.3),
+        None,
+    ),
+    "hyperball": ("MuonHyperball", dict(lr=0.05, momentum=0.9, hyperball_radius=2.0), None),
+    "muon_radial_brake": (
+        "Muon",
+        dict(lr=0.05, momentum=0.9, weight_decay=0.0),
+        ("RadialBrakeHook", dict(outward_scale=0.25, inward_scale=0.75)),
+    ),
+    "muon_relative_update": ("Muon", dict(lr=0.05, momentum=0.9), ("RelativeUpdateHook", dict())),
+}  # fmt: skip
+
+SPECTRAL_CASES = {
+    # name: (function, shape, seed, kwargs)
+    "clip_wide": ("spectral_clip", (32, 48), 500, dict(sigma_min=0.5, sigma_max=1.5)),
+    "clip_tall": ("spectral_clip", (48, 32), 501, dict(sigma_min=0.5, sigma_max=1.5)),
+    "clip_default": ("spectral_clip", (40, 40), 502, dict()),
+    "hardcap_wide": ("spectral_hardcap", (32, 48), 503, dict(beta=1.0)),
+    "hardcap_tall": ("spectral_hardcap", (48, 32), 504, dict(beta=0.8)),
+    "clipped_wd": ("spectral_clipped_weight_decay", (32, 48), 505, dict(beta=1.0, c=0.25)),
+}
+ONE_SIDED_CASES = {
+    "left": ((16, 64), 510, dict(side="left")),
+    "left_centered": ((16, 64), 511, dict(side="left", center_rows=True, alpha=0.5)),
+    "right": ((64, 16), 512, dict(side="right", extra_scale_factor=0.2)),
+    "right_centered": ((64, 16), 513, dict(side="right", center_rows=True)),
+}
+
+
+def make_consumers() -> None:
+    """Optimizers and utilities built on Newton-Schulz: three steps of each optimizer on three small matrices, at
+    "highest" and at "medium" precision; the spectral clipping functions; the one-sided polar updates."""
+    import emerging_optimizers.orthogonalized_optimizers as ref_opt
+    import emerging_optimizers.weight_update_hooks as ref_hooks
+    from emerging_optimizers.orthogonalized_optimizers import polargrad as ref_pg
+    from emerging_optimizers.orthogonalized_optimizers import spectral_clipping_utils as ref_sc
+
+    out = {}
+    for name, (cls, kw, hook) in CONSUMER_CASES.items():
+        for precision in ("highest", "medium"):
+            key = f"{name}.{precision}"
+            params = []
+            for i, s in enumerate(CONSUMER_SHAPES):
+                w = randn(*s, seed=400 + i, scale=0.05)
+                if cls == "MuonHyperball":
+                    w = w * (kw["hyperball_radius"] / w.norm())
+                params.append(torch.nn.Parameter(w))
+            extra = {} if hook is None else {"weight_update_hook": getattr(ref_hooks, hook[0])(**hook[1])}
+            opt = getattr(ref_opt, cls)(params, fp32_matmul_prec=precision, **kw, **extra)
+            # Initial weights and gradients are regenerated from their seeds by the tests, not stored.
+            for step in range(CONSUMER_STEPS):
+                for i, p in enumerate(params):
+                    p.grad = randn(*p.shape, seed=450 + 10 * step + i, scale=1e-2)
+                opt.step()
+                if step in (0, CONSUMER_STEPS - 1):
+                    for i, p in enumerate(params):
+                        out[f"{key}.p{i}.after{step}"] = p.detach().clone().numpy()
+            for i, p in enumerate(params):
+                for buf, t in opt.state[p].items():
+                    out[f"{key}.p{i}.{buf}"] = t.clone().numpy()
+
+    torch.set_float32_matmul_precision("highest")
+    for name, (fn, shape, seed, kw) in SPECTRAL_CASES.items():
+        x = randn(*shape, seed=seed, scale=0.2)
+        out[f"spectral.{name}"] = getattr(ref_sc, fn)(x, **kw).contiguous().numpy()
+    for name, (shape, seed, kw) in ONE_SIDED_CASES.items():
+        x = randn(*shape, seed=seed)
+        out[f"one_sided.{name}"] = ref_pg.one_sided_polargrad_orth_fn(x, **kw).contiguous().numpy()
+
+    np.savez_compressed(os.path.join(HERE, "consumers.npz"), **out)
+    with open(os.path.join(HERE, "consumer_cases.json"), "w") as f:
+        json.dump(
+            {
+                "shapes": CONSUMER_SHAPES,
+                "steps": CONSUMER_STEPS,
+                "optimizers": CONSUMER_CASES,
+                "spectral": SPECTRAL_CASES,
+                "one_sided": ONE_SIDED_CASES,
+            },
+            f,
+            indent=1,
+            sort_keys=True,
+        )
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
+    if sys.argv[1:] == ["consumers"]:
+        make_consumers()
+        raise SystemExit(0)
     make_tables()
     make_ns()
     make_config1()
     make_muon()
     make_tp()
+    make_consumers()
     for f in sorted(os.listdir(HERE)):
         print(f, os.path.getsize(os.path.join(HERE, f)))
