@@ -323,7 +323,33 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             "momentum_buffer": {i: st["momentum_buffer"] for i, st in self.state.items()},
         }
 
+    def gathered_state_dict(self) -> dict:
+        """The full checkpoint on every rank: each momentum buffer is broadcast by its owner.
+
+        Collective (all ranks of the group, same call order).  The result has the layout of :meth:`state_dict`
+        with every parameter index present, so it can be saved by one rank and later loaded on a group of any size:
+        :meth:`load_state_dict` keeps the entries of the matrices the loading rank owns.  Matrices that have not
+        been stepped yet have no entry.
+        """
+        full: dict[int, torch.Tensor] = {}
+        if self.world == 1:
+            full = {i: st["momentum_buffer"] for i, st in self.state.items()}
+            return {"owners": list(self.owners), "momentum_buffer": full}
+        # Which matrices have state is the same question on every rank only if the owners answer it.
+        has = torch.zeros(len(self.params), dtype=torch.int32, device=self.params[0].device if self.params else "cpu")
+        for i in self.state:
+            has[i] = 1
+        dist.all_reduce(has, op=dist.ReduceOp.MAX, group=self.group)
+        for i in has.nonzero().flatten().tolist():
+            p, owner = self.params[i], self.owners[i]
+            buf = self.state[i]["momentum_buffer"] if owner == self.rank else torch.empty_like(p.data)
+            dist.broadcast(buf, src=dist.get_global_rank(self.group, owner) if self.group is not None else owner,
+                           group=self.group)
+            full[i] = buf
+        return {"owners": list(self.owners), "momentum_buffer": full}
+
     def load_state_dict(self, sd: dict) -> None:
+        """Take (copies of) the momentum buffers of the matrices this rank owns; other entries are ignored."""
         for i, buf in sd["momentum_buffer"].items():
             if self.owners[int(i)] == self.rank:
-                self.state.setdefault(int(i), {})["momentum_buffer"] = buf.to(self.params[int(i)].device)
+                self.state.setdefault(int(i), {})["momentum_buffer"] = buf.to(self.params[int(i)].device, copy=True)

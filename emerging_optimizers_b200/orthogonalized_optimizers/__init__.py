@@ -1,5 +1,5 @@
 """Orthogonalized optimizers on the sm_100a Newton-Schulz kernels: the ``OrthogonalizedOptimizer`` base, ``Muon``
-and the optimizers derived from them (``AdaptiveMuon``, ``MuonHyperball``, ``PolarGrad``, ``Scion``, ``Spel``),
+and the optimizers derived from them (``AdaptiveMuon``, ``MuonHyperball``, ``PolarGrad``, ``Scion``, ``Spel``, ``SplitQkvMuon``),
 plus the ``muon_utils`` driver functions and ``spectral_clipping_utils``."""
 
 from emerging_optimizers_b200.orthogonalized_optimizers.adaptive_muon import *  # noqa: F401,F403
@@ -9,3 +9,4 @@ from emerging_optimizers_b200.orthogonalized_optimizers.orthogonalized_optimizer
 from emerging_optimizers_b200.orthogonalized_optimizers.polargrad import *  # noqa: F401,F403
 from emerging_optimizers_b200.orthogonalized_optimizers.scion import *  # noqa: F401,F403
 from emerging_optimizers_b200.orthogonalized_optimizers.spel import *  # noqa: F401,F403
+from emerging_optimizers_b200.orthogonalized_optimizers.split_qkv import *  # noqa: F401,F403

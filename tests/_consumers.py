@@ -64,3 +64,28 @@ def run_case(name, precision, device):
 def rel_fro(a, b):
     a, b = a.double(), b.double()
     return float((a - b).norm() / b.norm().clamp_min(1e-300))
+
+
+def run_split_qkv(name, precision, device):
+    """Two steps of SplitQkvMuon on a fused QKV weight and an ordinary weight; returns both weights (cpu) and
+    their initial values."""
+    cfg = CASES["split_qkv"]
+    split, groups, per_head, head_dim = cfg["cases"][name]
+    qkv0 = randn(groups * sum(split), cfg["hidden"], seed=600, scale=0.05)
+    other0 = randn(24, 40, seed=601, scale=0.05)
+    qkv, other = torch.nn.Parameter(qkv0.clone().to(device)), torch.nn.Parameter(other0.clone().to(device))
+    qkv.is_qkv = True
+    opt = opt_pkg.SplitQkvMuon(
+        [qkv, other],
+        qkv_split_shapes=split,
+        num_query_groups=groups,
+        per_head=per_head,
+        head_dim=head_dim,
+        fp32_matmul_prec=precision,
+        **cfg["muon"],
+    )
+    for step in range(2):
+        qkv.grad = randn(*qkv.shape, seed=610 + step, scale=1e-2).to(device)
+        other.grad = randn(*other.shape, seed=620 + step, scale=1e-2).to(device)
+        opt.step()
+    return {"qkv": qkv.detach().cpu(), "other": other.detach().cpu()}, {"qkv": qkv0, "other": other0}

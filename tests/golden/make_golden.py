@@ -228,6 +228,65 @@ ONE_SIDED_CASES = {
 }
 
 
+QKV_HIDDEN = 48
+QKV_CASES = {
+    # name: (rows of q, k, v in one query group; query groups; per-head; head_dim)
+    "stacked": ((32, 16, 16), 1, False, None),
+    "interleaved": ((16, 8, 8), 2, False, None),
+    "per_head": ((16, 8, 8), 2, True, 8),
+}
+QKV_MUON = dict(lr=0.05, momentum=0.9, weight_decay=0.01, nesterov=True, scale_mode="shape_scaling")
+
+
+def qkv_row_sets(split, groups, per_head, head_dim):
+    """Row indices of every logical matrix inside a fused QKV weight laid out [q_0; k_0; v_0; q_1; ...]."""
+    per_group = sum(split)
+    sets = []
+    offset = 0
+    for rows in split:
+        block = [g * per_group + offset + r for g in range(groups) for r in range(rows)]
+        if per_head:
+            sets += [block[i : i + head_dim] for i in range(0, len(block), head_dim)]
+        else:
+            sets.append(block)
+        offset += rows
+    return sets
+
+
+def make_split_qkv(out: dict) -> None:
+    """Fused-QKV Muon the way the docstring of the reference's base class sketches it: a subclass of the
+    reference's Muon that runs ``scaled_orthogonalize_fn`` on every logical matrix of a tagged parameter."""
+
+    class RefSplitQkvMuon(RefMuon):
+        def __init__(self, params, row_sets, **kw):
+            super().__init__(params, **kw)
+            self.row_sets = row_sets
+
+        def orthogonalize(self, p, grad, **kwargs):
+            if not getattr(p, "is_qkv", False):
+                return self.scaled_orthogonalize_fn(grad)
+            res = torch.empty_like(grad)
+            for rows in self.row_sets:
+                idx = torch.tensor(rows)
+                res[idx] = self.scaled_orthogonalize_fn(grad[idx])
+            return res
+
+    for name, (split, groups, per_head, head_dim) in QKV_CASES.items():
+        for precision in ("highest", "medium"):
+            qkv = torch.nn.Parameter(randn(groups * sum(split), QKV_HIDDEN, seed=600, scale=0.05))
+            qkv.is_qkv = True
+            other = torch.nn.Parameter(randn(24, 40, seed=601, scale=0.05))
+            opt = RefSplitQkvMuon(
+                [qkv, other], qkv_row_sets(split, groups, per_head, head_dim), fp32_matmul_prec=precision, **QKV_MUON
+            )
+            for step in range(2):
+                qkv.grad = randn(*qkv.shape, seed=610 + step, scale=1e-2)
+                other.grad = randn(*other.shape, seed=620 + step, scale=1e-2)
+                opt.step()
+            out[f"split_qkv.{name}.{precision}.qkv"] = qkv.detach().clone().numpy()
+            out[f"split_qkv.{name}.{precision}.other"] = other.detach().clone().numpy()
+
+
 def make_consumers() -> None:
     """Optimizers and utilities built on Newton-Schulz: three steps of each optimizer on three small matrices, at
     "highest" and at "medium" precision; the spectral clipping functions; the one-sided polar updates."""
@@ -268,6 +327,7 @@ def make_consumers() -> None:
         x = randn(*shape, seed=seed)
         out[f"one_sided.{name}"] = ref_pg.one_sided_polargrad_orth_fn(x, **kw).contiguous().numpy()
 
+    make_split_qkv(out)
     np.savez_compressed(os.path.join(HERE, "consumers.npz"), **out)
     with open(os.path.join(HERE, "consumer_cases.json"), "w") as f:
         json.dump(
@@ -277,6 +337,7 @@ def make_consumers() -> None:
                 "optimizers": CONSUMER_CASES,
                 "spectral": SPECTRAL_CASES,
                 "one_sided": ONE_SIDED_CASES,
+                "split_qkv": {"hidden": QKV_HIDDEN, "cases": QKV_CASES, "muon": QKV_MUON},
             },
             f,
             indent=1,

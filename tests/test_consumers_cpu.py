@@ -171,6 +171,32 @@ def test_spel_retracts_to_near_orthogonal(cpu_ns):
     assert torch.allclose(p.detach() @ p.detach().T, torch.eye(16), atol=5e-2)
 
 
+@pytest.mark.parametrize("precision", ["highest", "medium"])
+@pytest.mark.parametrize("name", sorted(_consumers.CASES["split_qkv"]["cases"]))
+def test_split_qkv_muon_matches_reference_per_piece(cpu_ns, name, precision):
+    want = _consumers.golden()
+    got, _ = _consumers.run_split_qkv(name, precision, "cpu")
+    for key, val in got.items():
+        ref = torch.from_numpy(want[f"split_qkv.{name}.{precision}.{key}"])
+        assert _consumers.rel_fro(val, ref) <= (1e-5 if precision == "highest" else 2e-3), key
+
+
+def test_split_qkv_muon_argument_checks(cpu_ns):
+    from emerging_optimizers_b200.orthogonalized_optimizers import SplitQkvMuon
+
+    w = torch.nn.Parameter(torch.randn(30, 16))
+    with pytest.raises(ValueError, match="three positive row counts"):
+        SplitQkvMuon([w], qkv_split_shapes=(8, 8))
+    with pytest.raises(ValueError, match="num_query_groups must be at least 1"):
+        SplitQkvMuon([w], qkv_split_shapes=(8, 8, 8), num_query_groups=0)
+    with pytest.raises(ValueError, match="per_head needs a head_dim"):
+        SplitQkvMuon([w], qkv_split_shapes=(8, 8, 8), per_head=True, head_dim=3)
+    opt = SplitQkvMuon([{"params": [w], "is_qkv": True}], qkv_split_shapes=(8, 8, 8))
+    w.grad = torch.randn_like(w)
+    with pytest.raises(ValueError, match="expected num_query_groups"):
+        opt.step()
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # weight-update hooks on their own
 # ---------------------------------------------------------------------------------------------------------------

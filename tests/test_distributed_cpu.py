@@ -134,10 +134,24 @@ def _worker_lp(rank, port, out, kw):
             p.grad = g.clone()
         opt.step()
     sd = opt.state_dict()
+    full = opt.gathered_state_dict()
+    full_momentum = {i: b.numpy().copy() for i, b in full["momentum_buffer"].items()}  # owned entries alias the state
+    # A fresh optimizer that loads the gathered checkpoint keeps exactly the entries it owns, and continues
+    # identically.
+    params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    opt2 = LayerParallelMuon(params2, bucket_numel=1024, **kw)
+    opt2.load_state_dict(full)
+    for o, ps in ((opt, params), (opt2, params2)):
+        for p, g in zip(ps, _grads(3)):
+            p.grad = g.clone()
+        o.step()
     out[rank] = {
         "params": [p.detach().numpy().copy() for p in params],
+        "params_resumed": [p.detach().numpy().copy() for p in params2],
         "owned": opt.owned_indices(),
         "state_keys": sorted(sd["momentum_buffer"]),
+        "full_momentum": full_momentum,
+        "resumed_keys": sorted(opt2.state),
         "n_buckets": len(opt.buckets),
     }
     dist.destroy_process_group()
@@ -154,6 +168,10 @@ def test_layer_parallel_muon_equals_single_process_bitwise(method, monkeypatch):
         for p, g in zip(ref_params, _grads(step)):
             p.grad = g.clone()
         ref.step()
+    ref_momentum = [ref.state[p]["momentum_buffer"].clone().numpy() for p in ref_params]
+    for p, g in zip(ref_params, _grads(3)):
+        p.grad = g.clone()
+    ref.step()
 
     with mp.Manager() as mgr:
         out = mgr.dict()
@@ -166,6 +184,12 @@ def test_layer_parallel_muon_equals_single_process_bitwise(method, monkeypatch):
     for i in range(len(SHAPES)):
         assert np.array_equal(results[0]["params"][i], results[1]["params"][i]), i
         assert np.array_equal(results[0]["params"][i], ref_params[i].detach().numpy()), i
+        # the gathered checkpoint holds every momentum buffer on every rank, equal to the single-process one
+        for rank in range(WORLD):
+            assert np.array_equal(results[rank]["full_momentum"][i], ref_momentum[i]), (rank, i)
+            assert np.array_equal(results[rank]["params_resumed"][i], ref_params[i].detach().numpy()), (rank, i)
+    for rank in range(WORLD):
+        assert results[rank]["resumed_keys"] == sorted(results[rank]["owned"])
 
 
 def test_partition_is_balanced_and_deterministic():

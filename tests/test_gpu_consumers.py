@@ -90,3 +90,41 @@ def test_one_sided_polar_update_matches_reference(name):
     y = polargrad.one_sided_polargrad_orth_fn(x, **kw)
     ref = torch.from_numpy(_consumers.golden()[f"one_sided.{name}"])
     assert _consumers.rel_fro(y.cpu(), ref) <= 1e-4
+
+
+@pytest.mark.parametrize("precision", ["highest", "medium"])
+@pytest.mark.parametrize("name", sorted(_consumers.CASES["split_qkv"]["cases"]))
+def test_split_qkv_muon_matches_reference_per_piece(name, precision):
+    want = _consumers.golden()
+    got, init = _consumers.run_split_qkv(name, precision, "cuda")
+    for key, val in got.items():
+        ref = torch.from_numpy(want[f"split_qkv.{name}.{precision}.{key}"])
+        err = _consumers.rel_fro(val - init[key], ref - init[key])
+        assert err <= TOL[precision], (key, err)
+    assert _native.read_device_status() == 0
+
+
+def test_split_qkv_per_head_runs_one_batched_call_per_step():
+    """80 heads of 128 x 1024 inside one fused weight: the heads go through the library as one stack."""
+    from emerging_optimizers_b200.orthogonalized_optimizers import SplitQkvMuon
+
+    heads, head_dim, hidden = (64, 8, 8), 128, 1024
+    w = torch.nn.Parameter(_consumers.randn(sum(heads) * head_dim, hidden, seed=9, scale=0.02).cuda())
+    w.is_qkv = True
+    opt = SplitQkvMuon(
+        [w], lr=0.02, qkv_split_shapes=[h * head_dim // 8 for h in heads], num_query_groups=8, per_head=True,
+        head_dim=head_dim, coefficient_type="polar_express", num_ns_steps=8, scale_mode="shape_scaling",
+    )  # fmt: skip
+    w.grad = _consumers.randn(*w.shape, seed=10, scale=1e-3).cuda()
+    before = w.detach().clone()
+    n0 = _native.launch_count
+    opt.step()
+    launches = _native.launch_count - n0
+    assert launches == 4, launches  # sum of squares (2 kernels), normalise + cast, all eight iterations in one
+    # every head's update is a 128 x 1024 polar factor (scale factor 1 for a wide matrix under "shape_scaling")
+    upd = (before * (1 - 0.02 * 0.01) - w.detach()) / 0.02
+    per_head = upd.view(8, -1, hidden).reshape(-1, head_dim, hidden)
+    gram = per_head @ per_head.mT
+    eye = torch.eye(head_dim, device="cuda")
+    assert float((gram - eye).abs().max()) < 0.1
+    assert _native.read_device_status() == 0
