@@ -88,6 +88,12 @@ _PROTOTYPES: dict[str, tuple] = {
         [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int]
         + [c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
     ),
+    "eo_newton_schulz_f32_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "eo_newton_schulz_f32": (
+        c_int,
+        [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_int]
+        + [c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+    ),
     "eo_tp_gram_inbox_bytes": (c_size_t, [c_int, c_int]),
     "eo_tp_gram_flag_count": (c_size_t, [c_int, c_int]),
     "eo_tp_gram_allreduce": (
@@ -533,7 +539,12 @@ def newton_schulz_bf16(
     nbytes = lib().eo_newton_schulz_workspace_bytes(batch, rows, cols)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
     abc = (c_float * (3 * len(schedule)))(*[v for t in schedule for v in t])
-    kernels = sum(3 if t[2] != 0.0 else 2 for t in schedule)
+    # Launch count as the library decides it: one persistent kernel for stacks of small wide matrices, else two or
+    # three tensor-core launches per iteration.
+    if FUSED_SMALL_MATRICES and rows <= 128 and rows <= cols and cols >= 256 and len(schedule) <= 16:
+        kernels = 1
+    else:
+        kernels = sum(3 if t[2] != 0.0 else 2 for t in schedule)
     with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
         rc = lib().eo_newton_schulz_bf16(
             x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
@@ -542,6 +553,29 @@ def newton_schulz_bf16(
             ws.data_ptr(), nbytes, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_bf16")
+    return out
+
+
+def newton_schulz_f32(x: torch.Tensor, schedule) -> torch.Tensor:
+    """Run the whole iteration loop of the fp32 path on a normalised fp32 iterate ``x`` ((B,) rows, cols,
+    row-major) with one library call (see ``eo_newton_schulz_f32``).  Returns a new contiguous fp32 tensor."""
+    require_cuda(x, "x")
+    assert x.dtype == torch.float32 and len(schedule) >= 1
+    batch = x.size(0) if x.dim() == 3 else 1
+    rows, cols = x.size(-2), x.size(-1)
+    mn, ld, bs = _mat_layout(x)
+    assert mn == 0, "x must be row-major"
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    nbytes = lib().eo_newton_schulz_f32_workspace_bytes(batch, rows, cols)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    abc = (c_float * (3 * len(schedule)))(*[v for t in schedule for v in t])
+    kernels = sum(6 if t[2] != 0.0 else 4 for t in schedule)
+    with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
+        rc = lib().eo_newton_schulz_f32(
+            x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
+            out.data_ptr(), cols, rows * cols, ws.data_ptr(), nbytes, _stream(x),
+        )  # fmt: skip
+    _check(rc, "eo_newton_schulz_f32")
     return out
 
 

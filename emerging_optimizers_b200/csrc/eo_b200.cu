@@ -693,6 +693,119 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
   return EO_OK;
 }
 
+namespace {
+// Workspace of the fp32 driver: bf16 planes of the iterate and of A / S, fp32 A and S, one fp32 temporary iterate.
+struct NsF32Layout {
+  int m, n;
+  int64_t ldxp, xp_stride, xp_plane;  // planes of the iterate, in its storage orientation (rows x cols)
+  int64_t ldm, a_stride;              // fp32 A and S
+  int64_t ldmp, mp_stride, mp_plane;  // planes of A / S
+  int64_t ldt, t_stride;              // fp32 temporary iterate
+  size_t off_xp, off_a, off_s, off_mp, off_t, total;
+};
+
+NsF32Layout ns_f32_layout(int batch, int rows, int cols) {
+  NsF32Layout L;
+  L.m = rows <= cols ? rows : cols;
+  L.n = rows <= cols ? cols : rows;
+  L.ldxp = round_up(cols, 8);
+  L.xp_stride = static_cast<int64_t>(rows) * L.ldxp;
+  L.xp_plane = round_up(static_cast<int64_t>(batch) * L.xp_stride, 128);
+  L.ldm = round_up(L.m, 4);
+  L.a_stride = static_cast<int64_t>(L.m) * L.ldm;
+  L.ldmp = round_up(L.m, 8);
+  L.mp_stride = static_cast<int64_t>(L.m) * L.ldmp;
+  L.mp_plane = round_up(static_cast<int64_t>(batch) * L.mp_stride, 128);
+  L.ldt = round_up(cols, 4);
+  L.t_stride = static_cast<int64_t>(rows) * L.ldt;
+  size_t off = 0;
+  auto take = [&off](size_t bytes) {
+    const size_t at = off;
+    off += (bytes + 255) / 256 * 256;
+    return at;
+  };
+  L.off_xp = take(static_cast<size_t>(3 * L.xp_plane) * 2);
+  L.off_a = take(static_cast<size_t>(batch) * L.a_stride * 4);
+  L.off_s = take(static_cast<size_t>(batch) * L.a_stride * 4);
+  L.off_mp = take(static_cast<size_t>(3 * L.mp_plane) * 2);
+  L.off_t = take(static_cast<size_t>(batch) * L.t_stride * 4);
+  L.total = off;
+  return L;
+}
+}  // namespace
+
+size_t eo_newton_schulz_f32_workspace_bytes(int batch, int rows, int cols) {
+  if (batch <= 0 || rows <= 0 || cols <= 0) return 0;
+  return ns_f32_layout(batch, rows, cols).total;
+}
+
+int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t ld, int64_t stride,
+                         const float* host_abc, int steps, float* out, int64_t ldo, int64_t strideo, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0 || steps < 1) return fail(EO_ERR_BAD_ARG, "bad size or steps < 1");
+  if (batch == 0 || rows == 0 || cols == 0) return EO_OK;
+  if (X == nullptr || out == nullptr || host_abc == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (ld < cols || ldo < cols) return fail(EO_ERR_BAD_ARG, "leading dimension smaller than cols");
+  const NsF32Layout L = ns_f32_layout(batch, rows, cols);
+  if (workspace == nullptr || workspace_bytes < L.total)
+    return fail(EO_ERR_WORKSPACE, "newton_schulz_f32 workspace: need %zu bytes, got %zu", L.total, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(EO_ERR_BAD_ARG, "workspace must be 256-byte aligned");
+  char* ws = static_cast<char*>(workspace);
+  void* Xp = ws + L.off_xp;
+  float* A = reinterpret_cast<float*>(ws + L.off_a);
+  float* S = reinterpret_cast<float*>(ws + L.off_s);
+  void* Mp = ws + L.off_mp;
+  float* T = reinterpret_cast<float*>(ws + L.off_t);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int tall = rows > cols ? 1 : 0;
+
+  const float* cur = X;
+  int64_t cur_ld = ld, cur_stride = stride;
+  for (int it = 0; it < steps; ++it) {
+    const float a = host_abc[3 * it], b = host_abc[3 * it + 1], c = host_abc[3 * it + 2];
+    int rc;
+    // planes of the iterate, in storage orientation
+    eo::launch_split3(cur, batch, rows, cols, cur_ld, cur_stride, Xp, L.ldxp, L.xp_stride, L.xp_plane, st);
+    EO_CUDA(cudaGetLastError());
+    // A = X X^T over the wide orientation, lower triangle computed and mirrored
+    rc = launch_gemm(Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, nullptr, 0, 0, A,
+                     L.ldm, L.a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 1, 1, 0, 1, 0, stream);
+    if (rc) return rc;
+    eo::launch_split3(A, batch, L.m, L.m, L.ldm, L.a_stride, Mp, L.ldmp, L.mp_stride, L.mp_plane, st);
+    EO_CUDA(cudaGetLastError());
+    float alpha = b, beta = a;
+    if (c != 0.0f) {
+      // S = b A + c A A, then its planes replace those of A
+      rc = launch_gemm(Mp, 0, L.ldmp, L.mp_stride, L.mp_plane, Mp, 0, L.ldmp, L.mp_stride, L.mp_plane, A, L.ldm,
+                       L.a_stride, S, L.ldm, L.a_stride, batch, L.m, L.m, L.m, c, b, 1.0f, 1, 1, 0, 1, 0, stream);
+      if (rc) return rc;
+      eo::launch_split3(S, batch, L.m, L.m, L.ldm, L.a_stride, Mp, L.ldmp, L.mp_stride, L.mp_plane, st);
+      EO_CUDA(cudaGetLastError());
+      alpha = 1.0f;
+    }
+    // The iterate alternates between `out` and the temporary so that the last step lands in `out`.
+    const bool to_out = ((steps - 1 - it) % 2) == 0;
+    float* dst = to_out ? out : T;
+    const int64_t dst_ld = to_out ? ldo : L.ldt, dst_stride = to_out ? strideo : L.t_stride;
+    if (!tall) {
+      // X' = beta X + alpha S X: S is the K-major A operand, X (m x n row-major) the MN-major B operand
+      rc = launch_gemm(Mp, 0, L.ldmp, L.mp_stride, L.mp_plane, Xp, 1, L.ldxp, L.xp_stride, L.xp_plane, cur, cur_ld,
+                       cur_stride, dst, dst_ld, dst_stride, batch, L.m, L.n, L.m, alpha, beta, 1.0f, 1, 1, 0, 0, 0, stream);
+    } else {
+      // stored transposed (n x m): X'^T = beta X^T + alpha X^T S with S symmetric, both operands K-major
+      rc = launch_gemm(Xp, 0, L.ldxp, L.xp_stride, L.xp_plane, Mp, 0, L.ldmp, L.mp_stride, L.mp_plane, cur, cur_ld,
+                       cur_stride, dst, dst_ld, dst_stride, batch, L.n, L.m, L.m, alpha, beta, 1.0f, 1, 1, 0, 0, 0, stream);
+    }
+    if (rc) return rc;
+    cur = dst;
+    cur_ld = dst_ld;
+    cur_stride = dst_stride;
+  }
+  return EO_OK;
+}
+
 size_t eo_tp_gram_inbox_bytes(int N, int world) {
   if (N <= 0 || world <= 0) return 0;
   return static_cast<size_t>(world) * tp_slots(N, world) * eo::kBlockM * tp_tile_n(N) * 2;

@@ -406,21 +406,15 @@ def newton_schulz(
 
     native_fn = _NATIVE_STEP_FNS.get(ns_step_fn)
 
-    # Whole loop in one library call when nothing needs to happen between the products: bf16 path, no Gram
-    # all-reduce, step functions not replaced, default orientation, TMA-addressable rows.
+    # Whole loop in one library call when nothing needs to happen between the products: no Gram all-reduce, step
+    # functions not replaced, default orientation and (bf16 path, which reads the iterate by TMA) addressable rows.
     X_phys = X.mT if transpose else X  # the input's own orientation
     natural = transpose == (X_phys.size(-2) > X_phys.size(-1))  # the library call transposes exactly when rows > cols
-    if (
-        native_fn is not None
-        and bf16_path
-        and tp_group is None
-        and schedule
-        and natural
-        and X_phys.stride(-1) == 1
-        and X_phys.size(-1) % 8 == 0
-        and (X_phys.dim() == 2 or X_phys.stride(0) % 8 == 0)
-    ):
+    one_call = native_fn is not None and tp_group is None and schedule and natural and X_phys.stride(-1) == 1
+    if one_call and bf16_path and X_phys.size(-1) % 8 == 0 and (X_phys.dim() == 2 or X_phys.stride(0) % 8 == 0):
         return _native.newton_schulz_bf16(X_phys, schedule, native_fn, out_dtype=torch.float32)
+    if one_call and not bf16_path:
+        return _native.newton_schulz_f32(X_phys, schedule)
 
     for i, (a, b, c) in enumerate(schedule):
         if native_fn is not None and bf16_path and i == len(schedule) - 1:

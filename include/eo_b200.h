@@ -250,6 +250,24 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same loop for the fp32 ("highest" / "high") path: `steps` iterations on a normalised fp32 iterate X (batch x
+ * rows x cols, row-major, ld / stride in elements; the Gram matrix is taken over the shorter side), every product
+ * computed on three bf16 planes per operand (see eo_split_f32) with fp32 accumulation, A, S and the iterate kept
+ * in fp32.  X is not modified; the result goes to `out` (ldo / strideo in elements), which also serves as a
+ * ping-pong buffer.  Per iteration: split X, A (lower-triangular kernel), split A, S (likewise; skipped when
+ * c == 0), split S, X' -- the same kernels in the same order as the per-step entry points, driven from one call
+ * so that the host cost of about thirty launches is paid in C rather than in the caller's interpreter.
+ * `workspace`: eo_newton_schulz_f32_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
+ *
+ * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 when
+ * torch.get_float32_matmul_precision() is not "medium" (:245-262 select the fp32 step functions).
+ */
+size_t eo_newton_schulz_f32_workspace_bytes(int batch, int rows, int cols);
+int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t ld, int64_t stride,
+                         const float* host_abc, int steps, float* out, int64_t ldo, int64_t strideo, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/*
  * Tensor-parallel Gram matrix with the all-reduce fused into the SYRK epilogue (one NVSwitch box, 2..8 ranks).
  *
  * Every rank holds a shard X_r (N x K_r, bf16; `x_trans` as `a_trans` of eo_syrk) of a matrix sharded along

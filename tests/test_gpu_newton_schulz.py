@@ -194,6 +194,31 @@ def test_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
         assert fast.shape == slow.shape and torch.equal(fast, slow)
 
 
+@pytest.mark.parametrize("shape", [(256, 640), (640, 256), (3, 128, 384), (2, 384, 128), (13, 21), (2, 21, 13)])
+@pytest.mark.parametrize("ctype,steps", [("simple", 5), ("cubic5", 5), ("polar_express", 2), ("quintic", 1)])
+def test_fp32_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
+    """The same for the fp32 path: the library's one-call loop issues the kernels the step functions issue."""
+    x = randn_tensor(*shape, seed=41)
+    names = ["newton_schulz_step", "batched_newton_schulz_step"]
+    with fp32_matmul_precision("highest"):
+        n0 = nat.launch_count
+        fast = muon_utils.newton_schulz(x, steps, ctype)
+        per_call = nat.launch_count - n0
+        saved = {n: getattr(muon_utils, n) for n in names}
+        try:
+            for n, fn in saved.items():
+                setattr(muon_utils, n, (lambda f: lambda X, a, b, c, tp_group=None: f(X, a, b, c, tp_group=tp_group))(fn))
+            n0 = nat.launch_count
+            slow = muon_utils.newton_schulz(x, steps, ctype)
+            per_step = nat.launch_count - n0
+        finally:
+            for n, fn in saved.items():
+                setattr(muon_utils, n, fn)
+    assert fast.shape == slow.shape and fast.dtype == torch.float32 and torch.equal(fast, slow)
+    assert per_call == per_step  # same kernels, counted the same way
+    assert nat.read_device_status() == 0
+
+
 @pytest.mark.parametrize(
     "shape", [(4, 128, 512), (3, 64, 1024), (2, 128, 8192), (5, 120, 520), (128, 4096), (300, 128, 256), (1, 8, 256)]
 )
