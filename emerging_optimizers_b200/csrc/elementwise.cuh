@@ -169,9 +169,11 @@ inline void launch_split3(const float* x, int batch, int64_t rows, int64_t cols,
 //   u(g, m', p) : g' = g + l2 * p;  m' = lerp(m, g', 1 - mu);  u = nesterov ? lerp(g', m', mu) : m'
 // with lerp(a, b, w) = |w| < 0.5 ? a + w (b - a) : b - (b - a)(1 - w)   (the formula torch.lerp uses).
 // ---------------------------------------------------------------------------------------------
+// Written with explicit fused multiply-adds, which is what the compiler makes of torch's expression: the result
+// must not depend on how the surrounding code happens to be contracted.
 __device__ __forceinline__ float lerp_f32(float a, float b, float w) {
-  const float d = b - a;
-  return (fabsf(w) < 0.5f) ? a + w * d : b - d * (1.0f - w);
+  const float d = __fsub_rn(b, a);
+  return (fabsf(w) < 0.5f) ? __fmaf_rn(w, d, a) : __fmaf_rn(-d, __fsub_rn(1.0f, w), b);
 }
 
 struct MuonEw {
@@ -185,6 +187,23 @@ __device__ __forceinline__ float muon_update(float g, float m_new, const MuonEw&
   return c.nesterov ? lerp_f32(g, m_new, c.momentum) : m_new;
 }
 
+// One float4 of pass 1: the new momentum values (returned through mv) and the sum of squares of the four updates.
+__device__ __forceinline__ double muon_momentum_quad(float4 gv, float4& mv, const MuonEw& c) {
+  const float w = c.one_minus_momentum;
+  mv.x = lerp_f32(mv.x, gv.x, w); mv.y = lerp_f32(mv.y, gv.y, w);
+  mv.z = lerp_f32(mv.z, gv.z, w); mv.w = lerp_f32(mv.w, gv.w, w);
+  const double u0 = muon_update(gv.x, mv.x, c), u1 = muon_update(gv.y, mv.y, c);
+  const double u2 = muon_update(gv.z, mv.z, c), u3 = muon_update(gv.w, mv.w, c);
+  return (u0 * u0 + u1 * u1) + (u2 * u2 + u3 * u3);
+}
+
+__device__ __forceinline__ float4 muon_add_l2(float4 gv, float4 pv, float l2) {
+  // g + l2 * p with one rounding, as torch's add(p, alpha=l2) computes it
+  gv.x = __fmaf_rn(l2, pv.x, gv.x); gv.y = __fmaf_rn(l2, pv.y, gv.y);
+  gv.z = __fmaf_rn(l2, pv.z, gv.z); gv.w = __fmaf_rn(l2, pv.w, gv.w);
+  return gv;
+}
+
 // Pass 1: momentum buffer update in place and per-block partial sums of u^2.
 __device__ __forceinline__ void muon_momentum_body(const float* __restrict__ g, float* __restrict__ m,
                                                    const float* __restrict__ p, long long numel, const MuonEw& c,
@@ -193,25 +212,36 @@ __device__ __forceinline__ void muon_momentum_body(const float* __restrict__ g, 
   const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
   const long long n4 = numel >> 2;
-  const float w = c.one_minus_momentum;
-  for (long long i = tid; i < n4; i += nthreads) {
-    float4 gv = __ldg(reinterpret_cast<const float4*>(g) + i);
-    float4 mv = reinterpret_cast<float4*>(m)[i];
-    if (c.l2 != 0.0f) {
-      const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
-      gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+  float4* m4 = reinterpret_cast<float4*>(m);
+  const bool l2 = c.l2 != 0.0f;
+  long long i = tid;
+  // Two grid strides per trip, every load issued before the first store: the in-place update of m would otherwise
+  // order each trip's loads behind the previous trip's store and halve the bytes in flight.
+  for (; i + nthreads < n4; i += 2 * nthreads) {
+    float4 g0 = __ldg(g4 + i), g1 = __ldg(g4 + i + nthreads);
+    float4 m0 = m4[i], m1 = m4[i + nthreads];
+    if (l2) {
+      g0 = muon_add_l2(g0, __ldg(p4 + i), c.l2);
+      g1 = muon_add_l2(g1, __ldg(p4 + i + nthreads), c.l2);
     }
-    mv.x = lerp_f32(mv.x, gv.x, w); mv.y = lerp_f32(mv.y, gv.y, w);
-    mv.z = lerp_f32(mv.z, gv.z, w); mv.w = lerp_f32(mv.w, gv.w, w);
-    reinterpret_cast<float4*>(m)[i] = mv;
-    const double u0 = muon_update(gv.x, mv.x, c), u1 = muon_update(gv.y, mv.y, c);
-    const double u2 = muon_update(gv.z, mv.z, c), u3 = muon_update(gv.w, mv.w, c);
-    acc += u0 * u0 + u1 * u1;
-    acc += u2 * u2 + u3 * u3;
+    acc += muon_momentum_quad(g0, m0, c);
+    m4[i] = m0;
+    acc += muon_momentum_quad(g1, m1, c);
+    m4[i + nthreads] = m1;
   }
+  for (; i < n4; i += nthreads) {
+    float4 gv = __ldg(g4 + i);
+    float4 mv = m4[i];
+    if (l2) gv = muon_add_l2(gv, __ldg(p4 + i), c.l2);
+    acc += muon_momentum_quad(gv, mv, c);
+    m4[i] = mv;
+  }
+  const float w = c.one_minus_momentum;
   for (long long i = (n4 << 2) + tid; i < numel; i += nthreads) {
     float gv = g[i];
-    if (c.l2 != 0.0f) gv += c.l2 * p[i];
+    if (c.l2 != 0.0f) gv = __fmaf_rn(c.l2, p[i], gv);
     const float mv = lerp_f32(m[i], gv, w);
     m[i] = mv;
     const double u = muon_update(gv, mv, c);
@@ -232,10 +262,7 @@ __device__ __forceinline__ void muon_normalize_body(const float* __restrict__ g,
   for (long long i = tid; i < n4; i += nthreads) {
     float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c.nesterov) gv = __ldg(reinterpret_cast<const float4*>(g) + i);
-    if (c.nesterov && c.l2 != 0.0f) {
-      const float4 pv = __ldg(reinterpret_cast<const float4*>(p) + i);
-      gv.x += c.l2 * pv.x; gv.y += c.l2 * pv.y; gv.z += c.l2 * pv.z; gv.w += c.l2 * pv.w;
-    }
+    if (c.nesterov && c.l2 != 0.0f) gv = muon_add_l2(gv, __ldg(reinterpret_cast<const float4*>(p) + i), c.l2);
     const float4 mv = __ldg(reinterpret_cast<const float4*>(m) + i);
     const float q0 = muon_update(gv.x, mv.x, c) / norm, q1 = muon_update(gv.y, mv.y, c) / norm;
     const float q2 = muon_update(gv.z, mv.z, c) / norm, q3 = muon_update(gv.w, mv.w, c) / norm;
@@ -250,7 +277,7 @@ __device__ __forceinline__ void muon_normalize_body(const float* __restrict__ g,
     float gv = 0.f;
     if (c.nesterov) {
       gv = g[i];
-      if (c.l2 != 0.0f) gv += c.l2 * p[i];
+      if (c.l2 != 0.0f) gv = __fmaf_rn(c.l2, p[i], gv);
     }
     out[i] = __float2bfloat16_rn(muon_update(gv, m[i], c) / norm);
   }
@@ -259,9 +286,10 @@ __device__ __forceinline__ void muon_normalize_body(const float* __restrict__ g,
 // Weight update: p <- (p + shrink * p) - lr * ((u * scale) * extra), the operation order of
 // `p.add_(p, alpha=shrink)` followed by `p.add_(u * scale * extra, alpha=-lr)`.
 __device__ __forceinline__ float muon_apply_one(float pv, float uv, float shrink, float scale, float extra, float lr) {
-  if (shrink != 0.0f) pv = pv + shrink * pv;
-  const float t = (uv * scale) * extra;
-  return pv + (-lr) * t;
+  // explicit roundings: each add(x, alpha=s) of torch is one fused multiply-add
+  if (shrink != 0.0f) pv = __fmaf_rn(shrink, pv, pv);
+  const float t = __fmul_rn(__fmul_rn(uv, scale), extra);
+  return __fmaf_rn(-lr, t, pv);
 }
 
 template <typename U>
