@@ -164,6 +164,44 @@ inline void launch_split3(const float* x, int batch, int64_t rows, int64_t cols,
   }
 }
 
+// Sum of `nparts` fp32 partial matrices (rows x cols, row stride ld, `part_stride` elements apart), in a fixed order,
+// written as fp32 and as three bf16 planes: the tail of a K-split product followed by split3 in one pass.
+__global__ void __launch_bounds__(kEwThreads)
+    sum_split3_kernel(const float* __restrict__ parts, int nparts, long long part_stride, long long rows,
+                      long long cols, long long ld, float* __restrict__ sum, __nv_bfloat16* __restrict__ out,
+                      long long ldo, long long plane_stride) {
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  const long long units = rows * cols;
+  for (long long u = tid; u < units; u += nthreads) {
+    const long long r = u / cols, c = u - r * cols;
+    const long long at = r * ld + c;
+    float v = parts[at];
+    for (int s = 1; s < nparts; ++s) v = __fadd_rn(v, parts[at + s * part_stride]);
+    sum[at] = v;
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(v);
+    const float r1 = v - __bfloat162float(h0);
+    const __nv_bfloat16 h1 = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(h1);
+    const __nv_bfloat16 h2 = __float2bfloat16_rn(r2);
+    const long long o = r * ldo + c;
+    out[o] = h0;
+    out[o + plane_stride] = h1;
+    out[o + 2 * plane_stride] = h2;
+  }
+}
+
+inline void launch_sum_split3(const float* parts, int nparts, int64_t part_stride, int64_t rows, int64_t cols,
+                              int64_t ld, float* sum, void* out, int64_t ldo, int64_t plane_stride,
+                              cudaStream_t stream) {
+  const long long total = static_cast<long long>(rows) * cols;
+  long long nblk = (total + kEwThreads * 4 - 1) / (kEwThreads * 4);
+  if (nblk < 1) nblk = 1;
+  if (nblk > 4096) nblk = 4096;
+  sum_split3_kernel<<<static_cast<unsigned>(nblk), kEwThreads, 0, stream>>>(
+      parts, nparts, part_stride, rows, cols, ld, sum, static_cast<__nv_bfloat16*>(out), ldo, plane_stride);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Muon step, elementwise parts, on flat contiguous fp32 arrays.
 //   u(g, m', p) : g' = g + l2 * p;  m' = lerp(m, g', 1 - mu);  u = nesterov ? lerp(g', m', mu) : m'

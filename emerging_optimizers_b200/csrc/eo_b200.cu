@@ -701,8 +701,22 @@ struct NsF32Layout {
   int64_t ldm, a_stride;              // fp32 A and S
   int64_t ldmp, mp_stride, mp_plane;  // planes of A / S
   int64_t ldt, t_stride;              // fp32 temporary iterate
-  size_t off_xp, off_a, off_s, off_mp, off_t, total;
+  size_t off_xp, off_a, off_s, off_mp, off_t, off_parts, total;
+  int max_ksplit;  // partial Gram matrices the workspace has room for
 };
+
+// K-split of the Gram product of a single small matrix.  A = X X^T of an m x n iterate has only
+// ceil(m/128) (ceil(m/128) + 1) / 2 lower-triangle tiles, each a loop over all of n (six plane pairs long on the
+// fp32 path): for m = 1024 that is 36 CTAs on `sms` SMs.  Splitting n into S slices that run as the S "batches" of
+// one launch fills the machine; the S partial matrices are summed by the pass that splits A into planes anyway.
+int ns_f32_ksplit(int batch, int m, int n, int sms) {
+  if (batch != 1) return 1;
+  const long long tm = (m + 127) / 128;
+  const long long tiles = tm * (tm + 1) / 2;
+  int S = 1;
+  while (S < 8 && tiles * (2 * S) <= sms && n / (2 * S) >= 1024 && n % (2 * S * 8) == 0) S *= 2;
+  return S;
+}
 
 NsF32Layout ns_f32_layout(int batch, int rows, int cols) {
   NsF32Layout L;
@@ -729,6 +743,8 @@ NsF32Layout ns_f32_layout(int batch, int rows, int cols) {
   L.off_s = take(static_cast<size_t>(batch) * L.a_stride * 4);
   L.off_mp = take(static_cast<size_t>(3 * L.mp_plane) * 2);
   L.off_t = take(static_cast<size_t>(batch) * L.t_stride * 4);
+  L.max_ksplit = ns_f32_ksplit(batch, L.m, L.n, 1 << 30);  // what the shape allows on any SM count
+  L.off_parts = L.max_ksplit > 1 ? take(static_cast<size_t>(L.max_ksplit) * L.a_stride * 4) : off;
   L.total = off;
   return L;
 }
@@ -760,6 +776,8 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
   float* T = reinterpret_cast<float*>(ws + L.off_t);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int tall = rows > cols ? 1 : 0;
+  const int ksplit = ns_f32_ksplit(batch, L.m, L.n, dev->sm_count);
+  float* parts = reinterpret_cast<float*>(ws + L.off_parts);
 
   const float* cur = X;
   int64_t cur_ld = ld, cur_stride = stride;
@@ -770,10 +788,21 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
     eo::launch_split3(cur, batch, rows, cols, cur_ld, cur_stride, Xp, L.ldxp, L.xp_stride, L.xp_plane, st);
     EO_CUDA(cudaGetLastError());
     // A = X X^T over the wide orientation, lower triangle computed and mirrored
-    rc = launch_gemm(Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, nullptr, 0, 0, A,
-                     L.ldm, L.a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 1, 1, 0, 1, 0, stream);
-    if (rc) return rc;
-    eo::launch_split3(A, batch, L.m, L.m, L.ldm, L.a_stride, Mp, L.ldmp, L.mp_stride, L.mp_plane, st);
+    if (ksplit > 1) {
+      // slices of the contraction dimension as the batches of one launch: n / ksplit columns of the wide
+      // orientation apart, which is that many rows of a tall (transposed) storage
+      const int kslice = L.n / ksplit;
+      const int64_t slice_stride = tall ? static_cast<int64_t>(kslice) * L.ldxp : kslice;
+      rc = launch_gemm(Xp, tall, L.ldxp, slice_stride, L.xp_plane, Xp, tall, L.ldxp, slice_stride, L.xp_plane, nullptr,
+                       0, 0, parts, L.ldm, L.a_stride, ksplit, L.m, L.m, kslice, 1.0f, 0.0f, 1.0f, 1, 1, 0, 1, 0, stream);
+      if (rc) return rc;
+      eo::launch_sum_split3(parts, ksplit, L.a_stride, L.m, L.m, L.ldm, A, Mp, L.ldmp, L.mp_plane, st);
+    } else {
+      rc = launch_gemm(Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, Xp, tall, L.ldxp, L.xp_stride, L.xp_plane, nullptr, 0,
+                       0, A, L.ldm, L.a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 1, 1, 0, 1, 0, stream);
+      if (rc) return rc;
+      eo::launch_split3(A, batch, L.m, L.m, L.ldm, L.a_stride, Mp, L.ldmp, L.mp_stride, L.mp_plane, st);
+    }
     EO_CUDA(cudaGetLastError());
     float alpha = b, beta = a;
     if (c != 0.0f) {

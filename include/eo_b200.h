@@ -257,6 +257,10 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
  * ping-pong buffer.  Per iteration: split X, A (lower-triangular kernel), split A, S (likewise; skipped when
  * c == 0), split S, X' -- the same kernels in the same order as the per-step entry points, driven from one call
  * so that the host cost of about thirty launches is paid in C rather than in the caller's interpreter.
+ * A single matrix (batch == 1) whose Gram matrix has too few tiles for the SMs gets its A product sliced along
+ * the contraction dimension (2, 4 or 8 slices as batches of one launch, fp32 partial matrices in the workspace,
+ * summed in a fixed order by the pass that splits A); results then differ from the per-step entry points by fp32
+ * summation order only.
  * `workspace`: eo_newton_schulz_f32_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
  *
  * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 when

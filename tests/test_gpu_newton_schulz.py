@@ -219,6 +219,27 @@ def test_fp32_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
     assert nat.read_device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(1024, 4096), (4096, 512), (640, 2048), (256, 8192)])
+def test_fp32_k_split_gram_agrees_with_step_by_step(shape):
+    """A single small matrix: the one-call fp32 loop slices the contraction dimension of the Gram product across
+    CTAs and sums the partial matrices in fp32; the step functions do not.  Same products, different summation
+    order, so agreement to fp32 round-off (amplified by five "simple" steps) rather than bit for bit."""
+    x = randn_tensor(*shape, seed=42)
+    names = ["newton_schulz_step", "batched_newton_schulz_step"]
+    with fp32_matmul_precision("highest"):
+        fast = muon_utils.newton_schulz(x, 5, "simple")
+        saved = {n: getattr(muon_utils, n) for n in names}
+        try:
+            for n, fn in saved.items():
+                setattr(muon_utils, n, (lambda f: lambda X, a, b, c, tp_group=None: f(X, a, b, c, tp_group=tp_group))(fn))
+            slow = muon_utils.newton_schulz(x, 5, "simple")
+        finally:
+            for n, fn in saved.items():
+                setattr(muon_utils, n, fn)
+    assert rel_fro(fast, slow) <= 2e-5, rel_fro(fast, slow)
+    assert nat.read_device_status() == 0
+
+
 @pytest.mark.parametrize(
     "shape", [(4, 128, 512), (3, 64, 1024), (2, 128, 8192), (5, 120, 520), (128, 4096), (300, 128, 256), (1, 8, 256)]
 )
