@@ -183,3 +183,25 @@ def test_run_to_run_determinism():
     first = tk.tsyrk_ex(a)
     for _ in range(10):
         assert torch.equal(tk.tsyrk_ex(a), first)
+
+
+@pytest.mark.parametrize("shape", [(256, 640), (640, 256), (100, 72)])
+def test_kronecker_factor_update_matches_fp64(shape):
+    """L <- lerp(L, G G^T, 1 - beta), R <- lerp(R, G^T G, 1 - beta): fp32 round-off against float64, symmetric."""
+    from emerging_optimizers_b200.legacy_soap import update_kronecker_factors
+
+    g = randn_tensor(*shape, seed=70)
+    L0 = randn_tensor(shape[0], shape[0], seed=71)
+    R0 = randn_tensor(shape[1], shape[1], seed=72)
+    L0, R0 = L0 + L0.T, R0 + R0.T
+    L, R = L0.clone(), R0.clone()
+    update_kronecker_factors([L, R], g, 0.95)
+    g64 = g.double()
+    L_ref = 0.95 * L0.double() + 0.05 * (g64 @ g64.T)
+    R_ref = 0.95 * R0.double() + 0.05 * (g64.T @ g64)
+    assert rel_fro(L, L_ref) <= 2e-6 and rel_fro(R, R_ref) <= 2e-6
+    assert torch.equal(L, L.T) and torch.equal(R, R.T)
+    if shape[0] != shape[1]:
+        with pytest.raises(ValueError, match="Kronecker factor must be"):
+            update_kronecker_factors([R, L], g, 0.95)
+    assert nat.read_device_status() == 0
