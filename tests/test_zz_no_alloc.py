@@ -10,7 +10,6 @@ therefore met with equality).  It is collected last so that a stop-at-first-fail
 everything else.
 """
 
-import ctypes
 
 import pytest
 import torch
