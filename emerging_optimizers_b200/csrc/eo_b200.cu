@@ -743,7 +743,9 @@ NsF32Layout ns_f32_layout(int batch, int rows, int cols) {
   L.off_s = take(static_cast<size_t>(batch) * L.a_stride * 4);
   L.off_mp = take(static_cast<size_t>(3 * L.mp_plane) * 2);
   L.off_t = take(static_cast<size_t>(batch) * L.t_stride * 4);
-  L.max_ksplit = ns_f32_ksplit(batch, L.m, L.n, 1 << 30);  // what the shape allows on any SM count
+  // The workspace size must not depend on the device: reserve what a 256-SM part would use (no larger one exists)
+  // and let the launch take the smaller of this and what its own SM count asks for.
+  L.max_ksplit = ns_f32_ksplit(batch, L.m, L.n, 256);
   L.off_parts = L.max_ksplit > 1 ? take(static_cast<size_t>(L.max_ksplit) * L.a_stride * 4) : off;
   L.total = off;
   return L;
@@ -776,7 +778,8 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
   float* T = reinterpret_cast<float*>(ws + L.off_t);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int tall = rows > cols ? 1 : 0;
-  const int ksplit = ns_f32_ksplit(batch, L.m, L.n, dev->sm_count);
+  int ksplit = ns_f32_ksplit(batch, L.m, L.n, dev->sm_count);
+  if (ksplit > L.max_ksplit) ksplit = L.max_ksplit;
   float* parts = reinterpret_cast<float*>(ws + L.off_parts);
 
   const float* cur = X;

@@ -55,6 +55,26 @@ def test_scratch_size_query_needs_no_gpu():
     assert lib.eo_sumsq_scratch_bytes(5, 8192, 28672) == 5 * one
 
 
+def test_newton_schulz_workspace_queries_need_no_gpu():
+    lib = _native.lib()
+    for fn in (lib.eo_newton_schulz_workspace_bytes, lib.eo_newton_schulz_f32_workspace_bytes):
+        assert fn(0, 128, 256) == 0 and fn(1, 0, 256) == 0
+        assert fn(2, 1024, 4096) >= 2 * fn(1, 1024, 4096) - 4 * 32 * 1024 * 1024  # grows with the batch
+        assert fn(1, 1024, 4096) == fn(1, 4096, 1024)  # a tall input is the same problem transposed
+    # bf16: A and S (m x m) plus one temporary iterate
+    assert lib.eo_newton_schulz_workspace_bytes(1, 1024, 4096) >= 2 * (2 * 1024 * 1024 + 1024 * 4096)
+    # fp32: three planes of the iterate and of A / S, fp32 A, S and temporary iterate ...
+    base = 3 * 2 * 1024 * 4096 + 2 * 4 * 1024 * 1024 + 3 * 2 * 1024 * 1024 + 4 * 1024 * 4096
+    single = lib.eo_newton_schulz_f32_workspace_bytes(1, 1024, 4096)
+    assert single % 256 == 0 and single >= base
+    # ... and, for a single small matrix only, room for the partial Gram matrices of the K-split (2, 4 or 8)
+    assert single - base >= 2 * 4 * 1024 * 1024
+    batched = lib.eo_newton_schulz_f32_workspace_bytes(4, 1024, 4096)
+    assert batched < 4 * base + 64 * 1024
+    big = lib.eo_newton_schulz_f32_workspace_bytes(1, 8192, 28672)
+    assert big < 3 * 2 * 8192 * 28672 + 2 * 4 * 8192 * 8192 + 3 * 2 * 8192 * 8192 + 4 * 8192 * 28672 + 64 * 1024
+
+
 def test_cpu_tensors_are_rejected_loudly():
     import torch
 
