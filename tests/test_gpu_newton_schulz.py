@@ -219,6 +219,32 @@ def test_fp32_single_call_loop_equals_step_by_step_bitwise(shape, ctype, steps):
     assert nat.read_device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(511, 513), (511, 257), (257, 513)])
+def test_fp32_path_elementwise_on_powers_of_two(shape):
+    """The construction of the reference's tightest Newton-Schulz test (tests/test_muon_utils.py:182-210): entries
+    that are powers of two, odd sizes, integer custom coefficients, two steps.  Every term is positive, so there is
+    no cancellation and the comparison can be elementwise and purely relative (atol 0).  The reference holds its
+    fp32 GEMMs to rtol 1e-6 there; the split-bf16 products accumulate in the tensor cores' fp32 adders and are held
+    to 1e-5 against a float64 restatement."""
+    g = torch.Generator(device="cpu").manual_seed(50)
+    x = (2.0 ** torch.randint(-10, -5, shape, generator=g).float()).cuda()
+    sets = [(3.0, 5.0, 7.0), (11.0, 13.0, 17.0)]
+    with fp32_matmul_precision("highest"):
+        y = muon_utils.newton_schulz(x, steps=2, coefficient_type="custom", custom_coefficient_sets=sets)
+    X = x.double()
+    if shape[0] > shape[1]:
+        X = X.mT
+    X = X / X.norm()
+    for a, b, c in sets:
+        A = X @ X.mT
+        X = a * X + (b * A + c * A @ A) @ X
+    if shape[0] > shape[1]:
+        X = X.mT
+    rel = ((y.double() - X).abs() / X.abs()).max().item()
+    assert rel <= 1e-5, rel
+    assert nat.read_device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(1024, 4096), (4096, 512), (640, 2048), (256, 8192)])
 def test_fp32_k_split_gram_agrees_with_step_by_step(shape):
     """A single small matrix: the one-call fp32 loop slices the contraction dimension of the Gram product across
