@@ -466,6 +466,7 @@ def run_muon_step(args) -> None:
     opt = LayerParallelMuon(params, lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True,
                             weight_decay_method="decoupled", num_ns_steps=5, scale_mode="shape_scaling",
                             coefficient_type="simple", fp32_matmul_prec="medium", use_syrk=True,
+                            exchange=args.lp_exchange,
                             **({"bucket_numel": args.bucket_numel} if args.bucket_numel else {}))  # fmt: skip
 
     def barrier() -> None:
@@ -510,7 +511,7 @@ def run_muon_step(args) -> None:
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"Muon step, Llama-3-8B-shaped parameter set ({layers} layers, {len(params)} matrices, "
                        f"{sum(p.numel() for p in params) / 1e9:.2f} G parameters), layer-parallel x{world}",
-                       "l2": "parameter set far larger than L2"},
+                       "exchange": args.lp_exchange, "l2": "parameter set far larger than L2"},
             "tflops_dense_eq": dense / (float(t[0]) / 1e3) / 1e12, "tflops_sym": sym / (float(t[0]) / 1e3) / 1e12,
             "params_identical_across_ranks": same, "gpu_launches": (_native.launch_count - launches0),
             "clocks": clocks, "device_status": status,
@@ -605,6 +606,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
     ap.add_argument("--tp-shard-poly-min-world", type=int, default=0,
                     help="tp_ns: smallest group that computes S = bA + cA^2 in row blocks per rank (0: library default)")
+    ap.add_argument("--lp-exchange", choices=["updates", "parameters"], default="updates",
+                    help="muon_step: what the layer-parallel optimizer all-gathers")
     ap.add_argument("--bucket-numel", type=int, default=0,
                     help="muon_step: elements per rank and exchange bucket (0: the optimizer's default)")
     args = ap.parse_args()

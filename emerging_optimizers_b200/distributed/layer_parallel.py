@@ -20,6 +20,11 @@ Design for one NVSwitch box (one process per GPU, NCCL through ``torch.distribut
   kernels); host ranks (gloo, used by the tests) call ``all_gather_into_tensor``.
 - Weight decay and ``p -= lr * scale * update`` are then applied by every rank to every matrix with the same fp32
   arithmetic, which makes the parameters bitwise identical across ranks and equal to the single-process result.
+- ``exchange="parameters"`` is the alternative in which only the owner applies the update and the *updated
+  parameters* travel (4 bytes per parameter instead of 2, but the update kernel touches 1/P of the parameters
+  instead of all of them, and that kernel is the part of the step that does not shrink with P).  On GPUs the
+  parameters are moved, once, into a symmetric buffer laid out like the exchange slots, so the owners' copy-engine
+  pushes land directly in the peers' parameter storage and the receiving side does no work at all.
 """
 
 from __future__ import annotations
@@ -115,6 +120,11 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier.
         exchange_dtype: dtype of the gathered updates.  ``None`` picks bf16 on the "medium" path (lossless there)
             and fp32 otherwise.
+        exchange: "updates" (default): all-gather the orthogonalized updates, every rank applies all of them.
+            "parameters": the owner alone applies its updates and the updated fp32 parameters are all-gathered.  On
+            GPUs the first step then moves every ``p.data`` into a symmetric buffer owned by this object (a
+            collective call; tensors that alias the old storage are not updated any more), and from then on peers
+            write the new values straight into that storage.
     """
 
     def __init__(
@@ -135,9 +145,13 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         group: "dist.ProcessGroup | None" = None,
         bucket_numel: int = 64 * 1024 * 1024,
         exchange_dtype: torch.dtype | None = None,
+        exchange: str = "updates",
     ) -> None:
         if num_ns_steps < 1:
             raise ValueError(f"num_ns_steps must be at least 1, got {num_ns_steps}")
+        if exchange not in ("updates", "parameters"):
+            raise ValueError(f"exchange must be 'updates' or 'parameters', got {exchange!r}")
+        self.exchange = exchange
         self.params = list(params)
         for p in self.params:
             if p.ndim != 2:
@@ -158,6 +172,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         self.state: dict[int, dict[str, torch.Tensor]] = {}
         self._side: "torch.cuda.Stream | None" = None
         self._peer = None  # symmetric exchange buffer, created collectively at the first multi-GPU step
+        self._param_peer = None  # exchange="parameters": the symmetric buffer the parameters live in
         self._exchanges = 0
 
     # -- pieces of the step ------------------------------------------------------------------------------
@@ -252,6 +267,9 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             return
 
         dev = self.params[0].device
+        if self.exchange == "parameters":
+            self._step_exchanging_parameters(fused, dev)
+            return
         if dev.type != "cuda":
             # Host ranks (tests on gloo): plain collective, no overlap.
             for b in self.buckets:
@@ -293,6 +311,89 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
                     orths[i].record_stream(side)
                 peer.all_gather_slots(base, b.slot_numel)
                 self._apply_bucket(b, peer.local[base : base + self.world * b.slot_numel], fused)
+        torch.cuda.current_stream().wait_stream(side)
+
+    # -- exchange="parameters" ---------------------------------------------------------------------------
+    def _apply_owned(self, idxs: Sequence[int], orths: dict[int, torch.Tensor], fused: bool) -> None:
+        """The weight update of this rank's own matrices (the arithmetic of the single-process step)."""
+        if fused and idxs:
+            scales = [get_muon_scale_factor(*self.params[i].shape[-2:], mode=self.scale_mode) for i in idxs]
+            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
+            _native.muon_apply_batch(
+                [self.params[i].data for i in idxs], [orths[i] for i in idxs], scales, shrink,
+                self.extra_scale_factor, self.lr,
+            )  # fmt: skip
+            return
+        for i in idxs:
+            self._apply(i, orths[i], fused)
+
+    def _bucket_bases(self) -> list[int]:
+        """Element offset of every bucket in the flat parameter buffer (bucket-major, then rank, then slot offset)."""
+        bases, at = [], 0
+        for b in self.buckets:
+            bases.append(at)
+            at += self.world * b.slot_numel
+        return bases + [at]
+
+    def _adopt_parameters(self, dev: torch.device) -> None:
+        """Move every parameter into one symmetric fp32 buffer laid out like the exchange slots (collective)."""
+        from emerging_optimizers_b200.distributed.peer_memory import PeerBuffer
+
+        bases = self._bucket_bases()
+        self._param_peer = PeerBuffer(max(bases[-1], 8), torch.float32, dev, self.group)
+        for b, base in zip(self.buckets, bases):
+            for r in range(self.world):
+                for i, off in b.per_rank[r]:
+                    p = self.params[i]
+                    if p.dtype != torch.float32 or not p.data.is_contiguous():
+                        raise TypeError("exchange='parameters' needs contiguous float32 parameters")
+                    at = base + r * b.slot_numel + off
+                    home = self._param_peer.local[at : at + p.numel()].view_as(p.data)
+                    home.copy_(p.data)
+                    p.data = home
+        # Nobody may push into a rank's buffer before that rank has moved its parameters in.
+        torch.cuda.current_stream(dev).synchronize()
+        self._param_peer.barrier()
+        self._side = torch.cuda.Stream(device=dev)
+
+    def _step_exchanging_parameters(self, fused: bool, dev: torch.device) -> None:
+        if dev.type != "cuda":
+            # Host ranks (tests on gloo): the owners' new values are gathered and copied over the other ranks' copies.
+            for b in self.buckets:
+                mine = [i for i, _ in b.per_rank[self.rank]]
+                self._apply_owned(mine, self._orthogonalize_many(mine, fused), fused)
+                slot = torch.zeros(b.slot_numel, dtype=torch.float32, device=dev)
+                for i, off in b.per_rank[self.rank]:
+                    slot[off : off + self.params[i].numel()].copy_(self.params[i].data.reshape(-1))
+                gathered = torch.empty(self.world * b.slot_numel, dtype=torch.float32, device=dev)
+                dist.all_gather_into_tensor(gathered, slot, group=self.group)
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    for i, off in b.per_rank[r]:
+                        p = self.params[i]
+                        p.data.copy_(gathered[r * b.slot_numel + off : r * b.slot_numel + off + p.numel()].view_as(p))
+            return
+
+        # GPU ranks: the parameters live in the symmetric buffer, a rank's matrices of one bucket contiguously in
+        # its slot.  After the owner has updated them, pushing the slot to every peer (copy engines, side stream)
+        # IS the parameter update of the peers; it overlaps the Newton-Schulz work of the next bucket.  During a
+        # step a rank reads only matrices it owns, and peers write only matrices it does not own.
+        if self._param_peer is None:
+            self._adopt_parameters(dev)
+        peer, side = self._param_peer, self._side
+        # Entry barrier: a peer may write my copy of its matrices only after everything I enqueued before this step
+        # (the backward pass that read them) is done, and symmetrically.
+        peer.barrier()
+        for b, base in zip(self.buckets, self._bucket_bases()):
+            mine = [i for i, _ in b.per_rank[self.rank]]
+            orths = self._orthogonalize_many(mine, fused)
+            self._apply_owned(mine, orths, fused)
+            ready = torch.cuda.Event()
+            ready.record()
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                peer.all_gather_slots(base, b.slot_numel)
         torch.cuda.current_stream().wait_stream(side)
 
     def _apply_bucket(self, b: _Bucket, gathered: torch.Tensor, fused: bool) -> None:

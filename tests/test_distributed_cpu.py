@@ -123,12 +123,12 @@ def _grads(step):
     return [(torch.randn(*s, generator=g) * 1e-3).bfloat16().float() for s in SHAPES]
 
 
-def _worker_lp(rank, port, out, kw):
+def _worker_lp(rank, port, out, kw, exchange="updates"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=WORLD)
     muon_utils.newton_schulz = _cpu_ns
     params = _make_params()
-    opt = LayerParallelMuon(params, bucket_numel=1024, **kw)
+    opt = LayerParallelMuon(params, bucket_numel=1024, exchange=exchange, **kw)
     for step in range(3):
         for p, g in zip(params, _grads(step)):
             p.grad = g.clone()
@@ -139,7 +139,7 @@ def _worker_lp(rank, port, out, kw):
     # A fresh optimizer that loads the gathered checkpoint keeps exactly the entries it owns, and continues
     # identically.
     params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
-    opt2 = LayerParallelMuon(params2, bucket_numel=1024, **kw)
+    opt2 = LayerParallelMuon(params2, bucket_numel=1024, exchange=exchange, **kw)
     opt2.load_state_dict(full)
     for o, ps in ((opt, params), (opt2, params2)):
         for p, g in zip(ps, _grads(3)):
@@ -157,8 +157,8 @@ def _worker_lp(rank, port, out, kw):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("method", ["decoupled", "l2"])
-def test_layer_parallel_muon_equals_single_process_bitwise(method, monkeypatch):
+@pytest.mark.parametrize("method,exchange", [("decoupled", "updates"), ("l2", "updates"), ("decoupled", "parameters"), ("l2", "parameters")])
+def test_layer_parallel_muon_equals_single_process_bitwise(method, exchange, monkeypatch):
     kw = dict(KW, weight_decay_method=method)
     # single-process specification: this package's Muon with the same injected CPU orthogonalizer
     monkeypatch.setattr(muon_utils, "newton_schulz", _cpu_ns)
@@ -175,7 +175,7 @@ def test_layer_parallel_muon_equals_single_process_bitwise(method, monkeypatch):
 
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker_lp, args=(_free_port(), out, kw), nprocs=WORLD, join=True)
+        mp.spawn(_worker_lp, args=(_free_port(), out, kw, exchange), nprocs=WORLD, join=True)
         results = dict(out)
     owned_all = sorted(results[0]["owned"] + results[1]["owned"])
     assert owned_all == list(range(len(SHAPES)))  # every matrix has exactly one owner

@@ -127,13 +127,13 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _lp_worker(rank, world, port, out):
+def _lp_worker(rank, world, port, out, exchange="updates"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     dev = f"cuda:{rank}"
     params = _params(dev)
-    opt = LayerParallelMuon(params, use_syrk=True, bucket_numel=100_000, **KW)
+    opt = LayerParallelMuon(params, use_syrk=True, bucket_numel=100_000, exchange=exchange, **KW)
     for step in range(2):
         _set_grads(params, step)
         opt.step()
@@ -145,7 +145,8 @@ def _lp_worker(rank, world, port, out):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_layer_parallel_two_gpus_equals_single_process_bitwise():
+@pytest.mark.parametrize("exchange", ["updates", "parameters"])
+def test_layer_parallel_two_gpus_equals_single_process_bitwise(exchange):
     world = 2
     ref_params = _params()
     ref = Muon(ref_params, use_syrk=True, **KW)
@@ -154,7 +155,7 @@ def test_layer_parallel_two_gpus_equals_single_process_bitwise():
         ref.step()
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_lp_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        mp.spawn(_lp_worker, args=(world, _free_port(), out, exchange), nprocs=world, join=True)
         results = dict(out)
     assert sorted(results[0]["owned"] + results[1]["owned"]) == list(range(len(SHAPES)))
     for r in range(world):
