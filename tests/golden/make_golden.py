@@ -209,6 +209,7 @@ CONSUMER_CASES = {
         ("RadialBrakeHook", dict(outward_scale=0.25, inward_scale=0.75)),
     ),
     "muon_relative_update": ("Muon", dict(lr=0.05, momentum=0.9), ("RelativeUpdateHook", dict())),
+    "mop": ("MOP", dict(lr=0.05, momentum=0.9, nesterov=True, extra_scale_factor=0.5), None),
 }  # fmt: skip
 
 SPECTRAL_CASES = {

@@ -14,6 +14,7 @@ import torch
 
 from emerging_optimizers_b200 import registry
 from emerging_optimizers_b200.orthogonalized_optimizers import (
+    MOP,
     AdaptiveMuon,
     Muon,
     MuonHyperball,
@@ -100,7 +101,7 @@ def test_one_sided_polar_update_is_a_polar_factor():
 def test_registry_and_constructor_errors():
     for name, cls in (
         ("scion", Scion), ("spel", Spel), ("polargrad", PolarGrad), ("adaptive_muon", AdaptiveMuon),
-        ("muon_hyperball", MuonHyperball), ("muon", Muon),
+        ("muon_hyperball", MuonHyperball), ("muon", Muon), ("mop", MOP),
     ):  # fmt: skip
         assert registry.get_optimizer_cls(name) is cls
     w = [torch.nn.Parameter(torch.ones(4, 8))]

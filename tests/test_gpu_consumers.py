@@ -25,8 +25,9 @@ pytestmark = pytest.mark.gpu
 TOL = {"highest": 1e-4, "medium": 1e-2}
 
 
+# MOP takes its polar factor from the library SVD, not from the kernels of this package: covered on the CPU side only.
 @pytest.mark.parametrize("precision", ["highest", "medium"])
-@pytest.mark.parametrize("name", _consumers.OPTIMIZER_CASES)
+@pytest.mark.parametrize("name", [n for n in _consumers.OPTIMIZER_CASES if n != "mop"])
 def test_optimizer_steps_match_reference(name, precision):
     want = _consumers.golden()
     got, init = _consumers.run_case(name, precision, "cuda")
