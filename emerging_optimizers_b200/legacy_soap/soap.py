@@ -17,7 +17,9 @@ __all__ = ["update_kronecker_factors"]
 
 
 @torch.no_grad()
-def update_kronecker_factors(kronecker_factor_list: list[torch.Tensor], grad: torch.Tensor, shampoo_beta: float) -> None:
+def update_kronecker_factors(
+    kronecker_factor_list: list[torch.Tensor], grad: torch.Tensor, shampoo_beta: float
+) -> None:
     """Update the left and right preconditioner statistics of a 2-D gradient in place.
 
     Args:

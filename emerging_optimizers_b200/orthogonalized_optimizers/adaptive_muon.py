@@ -49,7 +49,8 @@ class AdaptiveMuon(OrthogonalizedOptimizer):
         fp32_matmul_prec: fp32 matmul precision while orthogonalizing.
         coefficient_type: Newton-Schulz schedule name.
         num_ns_steps: number of Newton-Schulz iterations (at least 1).
-        scale_mode: Muon update scale, see :func:`~emerging_optimizers_b200.orthogonalized_optimizers.muon.get_muon_scale_factor`.
+        scale_mode: Muon update scale, see
+            :func:`~emerging_optimizers_b200.orthogonalized_optimizers.muon.get_muon_scale_factor`.
         extra_scale_factor: extra multiplier of the update.
         moment2_method: "adamuon", "normuon" or "namo".
         beta2: EMA coefficient of the second moment (per-group default).

@@ -225,7 +225,9 @@ def _apply(
 TP_SHARD_GRAM_POLY_MIN_WORLD = 4
 
 
-def _gram_poly_sharded(A: torch.Tensor, b: float, c: float, tp_group: "torch.distributed.ProcessGroup") -> torch.Tensor | None:
+def _gram_poly_sharded(
+    A: torch.Tensor, b: float, c: float, tp_group: "torch.distributed.ProcessGroup"
+) -> torch.Tensor | None:
     """S = b A + c A A with the rows of S divided among the ranks of ``tp_group`` and all-gathered in place.
 
     Returns ``None`` when the split does not apply (small group, batched or fp32 iterate, rows not divisible).

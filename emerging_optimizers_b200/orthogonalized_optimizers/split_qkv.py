@@ -110,5 +110,8 @@ class SplitQkvMuon(Muon):
                 results[i] = out[start : start + n]
                 start += n
 
-        merged = [r.reshape(groups, rows, hidden) for r, rows in zip(results, self.qkv_split_shapes)]  # type: ignore[union-attr]
+        merged = [
+            r.reshape(groups, rows, hidden)  # type: ignore[union-attr]
+            for r, rows in zip(results, self.qkv_split_shapes)
+        ]
         return torch.cat(merged, dim=1).reshape(groups * per_group, hidden)
