@@ -182,6 +182,46 @@ def test_split_qkv_muon_matches_reference_per_piece(cpu_ns, name, precision):
         assert _consumers.rel_fro(val, ref) <= (1e-5 if precision == "highest" else 2e-3), key
 
 
+@pytest.mark.parametrize("groups,split,per_head,head_dim", [
+    (1, (6, 2, 2), False, None), (3, (4, 2, 2), False, None), (3, (4, 2, 2), True, 2), (2, (8, 4, 4), True, 4),
+    (4, (2, 2, 2), True, 1), (1, (5, 3, 7), False, None),
+])  # fmt: skip
+def test_split_qkv_routes_every_row_to_its_own_logical_matrix(groups, split, per_head, head_dim):
+    """The layout algebra on its own: with an 'orthogonalizer' that just tags every matrix it is handed, each row of
+    the fused weight must come back tagged by the logical matrix the explicit index arithmetic assigns it to, and
+    the values themselves must return to their rows."""
+    from emerging_optimizers_b200.orthogonalized_optimizers import SplitQkvMuon
+
+    hidden, per_group = 5, sum(split)
+    rows = groups * per_group
+    grad = torch.arange(rows * hidden, dtype=torch.float32).reshape(rows, hidden)
+    p = torch.nn.Parameter(torch.zeros(rows, hidden))
+    p.is_qkv = True
+    opt = SplitQkvMuon([p], qkv_split_shapes=split, num_query_groups=groups, per_head=per_head, head_dim=head_dim)
+    seen = []
+
+    def tagger(x):
+        # one call may carry a stack of equally shaped matrices: tag each matrix by the rows it contains
+        mats = x if x.dim() == 3 else x.unsqueeze(0)
+        for m in mats:
+            seen.append(sorted(int(v) // hidden for v in m[:, 0].tolist()))
+        return x.clone()
+
+    opt.scaled_orthogonalize_fn = tagger
+    out = opt.orthogonalize(p, grad)
+    assert torch.equal(out, grad)  # identity on the values: every row went back to where it came from
+    want = []
+    offset = 0
+    for block in split:
+        rows_of_block = [g * per_group + offset + r for g in range(groups) for r in range(block)]
+        if per_head:
+            want += [rows_of_block[i : i + head_dim] for i in range(0, len(rows_of_block), head_dim)]
+        else:
+            want.append(rows_of_block)
+        offset += block
+    assert sorted(seen) == sorted(want)
+
+
 def test_split_qkv_muon_argument_checks(cpu_ns):
     from emerging_optimizers_b200.orthogonalized_optimizers import SplitQkvMuon
 
