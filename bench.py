@@ -406,9 +406,9 @@ def run_gpu_arm(args) -> None:
                 "unit": "TFLOP/s",
                 "frac": (achieved / peak) if achieved else None,
                 "frac_of_burst_peak": (achieved / float(peaks["bf16_tflops"])) if achieved else None,
-                # DRAM bytes per launch, from the ncu capture of one iteration on 4096 x 16384 (read + write of the
-                # Gram, A^2 and BX launches: 138 + 35 + 398 MB) scaled by operand bytes to this shape and averaged
-                # over the three launches (the capture is summarised under profiles/).
+                # DRAM bytes per launch: read + write of the Gram, A^2 and BX launches of one iteration measured by
+                # ncu on 4096 x 16384 (138 + 35 + 398 MB), scaled by operand bytes to this shape and averaged over
+                # the three launches.
                 "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
                 "algorithmic_flops_per_launch": sym * 2 / n_launch if n_launch else None,
                 "avg_launch_ms": k_total_ms / n_launch if n_launch else None,

@@ -30,10 +30,11 @@ Design for one NVSwitch box (one process per GPU, NCCL through ``torch.distribut
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Iterable, Sequence
+from typing import Sequence
 
 import torch
 import torch.distributed as dist
+from torch.optim.optimizer import ParamsT
 
 from emerging_optimizers_b200 import _native, mixin, utils
 from emerging_optimizers_b200.orthogonalized_optimizers import _fused_step, muon_utils
@@ -107,20 +108,25 @@ def _plan_buckets(numels: Sequence[int], owners: Sequence[int], world: int, buck
     return buckets
 
 
-class LayerParallelMuon(mixin.WeightDecayMixin):
+class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
     """Muon over 2-D parameters with the Newton-Schulz work divided among the ranks of ``group``.
 
-    Hyper-parameters have the meaning they have for :class:`~emerging_optimizers_b200.orthogonalized_optimizers.Muon`.
-    ``step()`` must be called by all ranks of the group, with identical gradients on all of them.
+    A ``torch.optim.Optimizer``: ``params`` may be an iterable of parameters or of parameter-group dicts, the
+    per-group ``lr``, ``momentum`` and ``weight_decay`` are honoured (so learning-rate schedulers work),
+    ``zero_grad`` and ``add_param_group``-free use behave as usual, and the per-parameter state key is
+    ``"momentum_buffer"`` as in ``orthogonalized_optimizer.py:136-154`` of the reference; a rank holds state only
+    for the matrices it owns.  The remaining hyper-parameters have the meaning they have for
+    :class:`~emerging_optimizers_b200.orthogonalized_optimizers.Muon`.  ``step()`` must be called by all ranks of the
+    group, with identical gradients on all of them.
 
     Args:
-        params: the 2-D parameters, in the same order on every rank.
+        params: the 2-D parameters (or parameter groups), in the same order on every rank.
         group: process group to divide the work over (``None``: the default group; a single process if
             torch.distributed is not initialised).
         bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier.
         exchange_dtype: dtype of the gathered updates.  ``None`` picks bf16 on the "medium" path (lossless there)
             and fp32 otherwise.
-        exchange: "updates" (default): all-gather the orthogonalized updates, every rank applies all of them.
+        exchange: "updates": all-gather the orthogonalized updates, every rank applies all of them.
             "parameters": the owner alone applies its updates and the updated fp32 parameters are all-gathered.  On
             GPUs the first step then moves every ``p.data`` into a symmetric buffer owned by this object (a
             collective call; tensors that alias the old storage are not updated any more), and from then on peers
@@ -129,7 +135,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
 
     def __init__(
         self,
-        params: Iterable[torch.nn.Parameter],
+        params: ParamsT,
         lr: float = 3e-4,
         momentum: float = 0.95,
         weight_decay: float = 0.01,
@@ -151,12 +157,15 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             raise ValueError(f"num_ns_steps must be at least 1, got {num_ns_steps}")
         if exchange not in ("updates", "parameters"):
             raise ValueError(f"exchange must be 'updates' or 'parameters', got {exchange!r}")
+        super().__init__(params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay))
         self.exchange = exchange
-        self.params = list(params)
+        # Flat view of the parameter groups: index i everywhere below is the position in this list, which is also
+        # the index torch's state_dict() packs the parameter under.
+        self.params = [p for g in self.param_groups for p in g["params"]]
+        self._group_of = [g for g in self.param_groups for _ in g["params"]]
         for p in self.params:
             if p.ndim != 2:
                 raise ValueError("Only 2D parameters are supported.")
-        self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.nesterov, self.weight_decay_method = nesterov, weight_decay_method
         self.fp32_matmul_prec = fp32_matmul_prec
         self.coefficient_type, self.num_ns_steps = coefficient_type, num_ns_steps
@@ -169,7 +178,6 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
 
         self.owners = partition_by_cost([ns_cost(p.shape) for p in self.params], self.world)
         self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel)
-        self.state: dict[int, dict[str, torch.Tensor]] = {}
         self._side: "torch.cuda.Stream | None" = None
         self._peer = None  # symmetric exchange buffer, created collectively at the first multi-GPU step
         self._param_peer = None  # exchange="parameters": the symmetric buffer the parameters live in
@@ -179,20 +187,38 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
     def owned_indices(self) -> list[int]:
         return [i for i, r in enumerate(self.owners) if r == self.rank]
 
+    def _hyper(self, i: int) -> tuple[float, float, float]:
+        """(lr, momentum, weight_decay) of parameter ``i``, read from its parameter group at call time."""
+        g = self._group_of[i]
+        return g["lr"], g["momentum"], g["weight_decay"]
+
+    def _shrink(self, i: int) -> float:
+        lr, _, wd = self._hyper(i)
+        return _SHRINK[self.weight_decay_method](lr, wd) if wd != 0.0 else 0.0
+
+    def _momentum_buffer(self, i: int) -> torch.Tensor:
+        st = self.state[self.params[i]]
+        if "momentum_buffer" not in st:
+            st["momentum_buffer"] = torch.zeros_like(self.params[i].data)
+        return st["momentum_buffer"]
+
+    def _by_group(self, idxs: Sequence[int]) -> list[list[int]]:
+        """``idxs`` split into runs that share a parameter group (one fused call each), order preserved."""
+        runs: dict[int, list[int]] = {}
+        for i in idxs:
+            runs.setdefault(id(self._group_of[i]), []).append(i)
+        return list(runs.values())
+
     def _orthogonalize_owned(self, i: int) -> torch.Tensor:
         """Momentum update, Nesterov and Newton-Schulz for parameter ``i`` (owned by this rank); unscaled."""
         p = self.params[i]
-        if p.grad is None:
-            raise RuntimeError(f"parameter {i} has no gradient; layer-parallel Muon needs all gradients")
+        _, momentum, wd = self._hyper(i)
         grad = p.grad
-        if self.weight_decay_method == "l2" and self.weight_decay != 0.0:
-            grad = grad.add(p, alpha=self.weight_decay)
-        st = self.state.setdefault(i, {})
-        if "momentum_buffer" not in st:
-            st["momentum_buffer"] = torch.zeros_like(p.data)
-        buf = st["momentum_buffer"]
-        buf.lerp_(grad, 1 - self.momentum)
-        update = grad.lerp(buf, self.momentum) if self.nesterov else buf
+        if self.weight_decay_method == "l2" and wd != 0.0:
+            grad = grad.add(p, alpha=wd)
+        buf = self._momentum_buffer(i)
+        buf.lerp_(grad, 1 - momentum)
+        update = grad.lerp(buf, momentum) if self.nesterov else buf
         with utils.fp32_matmul_precision(self.fp32_matmul_prec):
             return muon_utils.newton_schulz(
                 update, steps=self.num_ns_steps, coefficient_type=self.coefficient_type, use_syrk=self.use_syrk
@@ -213,39 +239,50 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         """Unscaled orthogonalized updates of the owned parameters ``idxs``."""
         if not fused:
             return {i: self._orthogonalize_owned(i) for i in idxs}
-        for i in idxs:
-            st = self.state.setdefault(i, {})
-            if "momentum_buffer" not in st:
-                st["momentum_buffer"] = torch.zeros_like(self.params[i].data)
-        l2 = self.weight_decay if self.weight_decay_method == "l2" else 0.0
-        ups = _fused_step.orthogonalized_updates(
-            [self.params[i].data for i in idxs],
-            [self.params[i].grad for i in idxs],
-            [self.state[i]["momentum_buffer"] for i in idxs],
-            momentum=self.momentum,
-            nesterov=self.nesterov,
-            l2_weight_decay=l2,
-            steps=self.num_ns_steps,
-            coefficient_type=self.coefficient_type,
-            use_syrk=self.use_syrk,
-        )
-        return dict(zip(idxs, ups))
+        out: dict[int, torch.Tensor] = {}
+        for run in self._by_group(idxs):
+            _, momentum, wd = self._hyper(run[0])
+            ups = _fused_step.orthogonalized_updates(
+                [self.params[i].data for i in run],
+                [self.params[i].grad for i in run],
+                [self._momentum_buffer(i) for i in run],
+                momentum=momentum,
+                nesterov=self.nesterov,
+                l2_weight_decay=wd if self.weight_decay_method == "l2" else 0.0,
+                steps=self.num_ns_steps,
+                coefficient_type=self.coefficient_type,
+                use_syrk=self.use_syrk,
+            )
+            out.update(zip(run, ups))
+        return out
 
-    def _apply(self, i: int, orth: torch.Tensor, fused: bool = False) -> None:
-        """Weight decay and ``p -= lr * (orth * scale * extra)`` with the arithmetic of the single-process step."""
-        p = self.params[i]
-        scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode)
-        if fused:
-            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
-            _native.muon_apply(p.data, orth, shrink, scale, self.extra_scale_factor, self.lr)
+    def _apply_many(self, idxs: Sequence[int], updates: Sequence[torch.Tensor], fused: bool) -> None:
+        """Weight decay and ``p -= lr * (update * scale * extra)`` for the parameters ``idxs``, with the arithmetic
+        of the single-process step; one fused launch sequence per parameter group."""
+        if not fused:
+            for i, u in zip(idxs, updates):
+                p = self.params[i]
+                lr, _, wd = self._hyper(i)
+                scale = get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode)
+                if self.weight_decay_method != "l2":
+                    self._apply_weight_decay_inplace(p.data, p.grad, lr, wd)
+                p.data.add_(u.view_as(p).to(torch.float32) * scale * self.extra_scale_factor, alpha=-lr)
             return
-        if self.weight_decay_method != "l2":
-            self._apply_weight_decay_inplace(p.data, p.grad, self.lr, self.weight_decay)
-        p.data.add_(orth.to(torch.float32) * scale * self.extra_scale_factor, alpha=-self.lr)
+        by_idx = dict(zip(idxs, updates))
+        for run in self._by_group(idxs):
+            lr = self._hyper(run[0])[0]
+            scales = [get_muon_scale_factor(*self.params[i].shape[-2:], mode=self.scale_mode) for i in run]
+            _native.muon_apply_batch(
+                [self.params[i].data for i in run], [by_idx[i] for i in run], scales, self._shrink(run[0]),
+                self.extra_scale_factor, lr,
+            )  # fmt: skip
 
     @torch.no_grad()
-    def step(self) -> None:
-        """One optimizer step; on return every rank holds the same updated parameters."""
+    def step(self, closure=None) -> None:  # type: ignore[no-untyped-def,override]
+        """One optimizer step; on return every rank holds the same updated parameters.  ``closure`` is not
+        supported and must be ``None`` (as for the single-process optimizers)."""
+        if closure is not None:
+            raise ValueError("closure is not supported")
         for i, p in enumerate(self.params):
             if p.grad is None:
                 raise RuntimeError(f"parameter {i} has no gradient; layer-parallel Muon needs all gradients")
@@ -254,16 +291,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             for b in self.buckets:
                 idxs = [i for i, _ in b.per_rank[0]]
                 orths = self._orthogonalize_many(idxs, fused)
-                if fused:
-                    scales = [get_muon_scale_factor(*self.params[i].shape[-2:], mode=self.scale_mode) for i in idxs]
-                    shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay else 0.0
-                    _native.muon_apply_batch(
-                        [self.params[i].data for i in idxs], [orths[i] for i in idxs], scales, shrink,
-                        self.extra_scale_factor, self.lr,
-                    )
-                else:
-                    for i in idxs:
-                        self._apply(i, orths[i], fused)
+                self._apply_many(idxs, [orths[i] for i in idxs], fused)
             return
 
         dev = self.params[0].device
@@ -314,19 +342,6 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         torch.cuda.current_stream().wait_stream(side)
 
     # -- exchange="parameters" ---------------------------------------------------------------------------
-    def _apply_owned(self, idxs: Sequence[int], orths: dict[int, torch.Tensor], fused: bool) -> None:
-        """The weight update of this rank's own matrices (the arithmetic of the single-process step)."""
-        if fused and idxs:
-            scales = [get_muon_scale_factor(*self.params[i].shape[-2:], mode=self.scale_mode) for i in idxs]
-            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
-            _native.muon_apply_batch(
-                [self.params[i].data for i in idxs], [orths[i] for i in idxs], scales, shrink,
-                self.extra_scale_factor, self.lr,
-            )  # fmt: skip
-            return
-        for i in idxs:
-            self._apply(i, orths[i], fused)
-
     def _bucket_bases(self) -> list[int]:
         """Element offset of every bucket in the flat parameter buffer (bucket-major, then rank, then slot offset)."""
         bases, at = [], 0
@@ -361,7 +376,8 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
             # Host ranks (tests on gloo): the owners' new values are gathered and copied over the other ranks' copies.
             for b in self.buckets:
                 mine = [i for i, _ in b.per_rank[self.rank]]
-                self._apply_owned(mine, self._orthogonalize_many(mine, fused), fused)
+                orths = self._orthogonalize_many(mine, fused)
+                self._apply_many(mine, [orths[i] for i in mine], fused)
                 slot = torch.zeros(b.slot_numel, dtype=torch.float32, device=dev)
                 for i, off in b.per_rank[self.rank]:
                     slot[off : off + self.params[i].numel()].copy_(self.params[i].data.reshape(-1))
@@ -388,7 +404,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         for b, base in zip(self.buckets, self._bucket_bases()):
             mine = [i for i, _ in b.per_rank[self.rank]]
             orths = self._orthogonalize_many(mine, fused)
-            self._apply_owned(mine, orths, fused)
+            self._apply_many(mine, [orths[i] for i in mine], fused)
             ready = torch.cuda.Event()
             ready.record()
             with torch.cuda.stream(side):
@@ -397,60 +413,52 @@ class LayerParallelMuon(mixin.WeightDecayMixin):
         torch.cuda.current_stream().wait_stream(side)
 
     def _apply_bucket(self, b: _Bucket, gathered: torch.Tensor, fused: bool) -> None:
-        if fused:
-            ps, us, scales = [], [], []
-            for r in range(self.world):
-                base = r * b.slot_numel
-                for i, off in b.per_rank[r]:
-                    p = self.params[i]
-                    ps.append(p.data)
-                    us.append(gathered[base + off : base + off + p.numel()])
-                    scales.append(get_muon_scale_factor(p.size(-2), p.size(-1), mode=self.scale_mode))
-            shrink = _SHRINK[self.weight_decay_method](self.lr, self.weight_decay) if self.weight_decay != 0.0 else 0.0
-            _native.muon_apply_batch(ps, us, scales, shrink, self.extra_scale_factor, self.lr)
-            return
+        idxs, ups = [], []
         for r in range(self.world):
             base = r * b.slot_numel
             for i, off in b.per_rank[r]:
-                p = self.params[i]
-                self._apply(i, gathered[base + off : base + off + p.numel()].view_as(p), fused)
+                idxs.append(i)
+                ups.append(gathered[base + off : base + off + self.params[i].numel()])
+        self._apply_many(idxs, ups, fused)
 
     # -- checkpointing -----------------------------------------------------------------------------------
-    def state_dict(self) -> dict:
-        """This rank's momentum buffers keyed by parameter index, plus the ownership map.  A full checkpoint is
-        the union over ranks."""
-        return {
-            "owners": list(self.owners),
-            "momentum_buffer": {i: st["momentum_buffer"] for i, st in self.state.items()},
-        }
+    # ``state_dict()`` is torch's: ``{"state": {index: {"momentum_buffer": tensor}}, "param_groups": [...]}`` with
+    # entries only for the matrices this rank owns (the union over ranks is the full checkpoint).
 
     def gathered_state_dict(self) -> dict:
-        """The full checkpoint on every rank: each momentum buffer is broadcast by its owner.
+        """The full checkpoint on every rank, in the layout of ``state_dict()``: each momentum buffer is broadcast
+        by its owner.
 
-        Collective (all ranks of the group, same call order).  The result has the layout of :meth:`state_dict`
-        with every parameter index present, so it can be saved by one rank and later loaded on a group of any size:
-        :meth:`load_state_dict` keeps the entries of the matrices the loading rank owns.  Matrices that have not
-        been stepped yet have no entry.
+        Collective (all ranks of the group, same call order).  Every stepped parameter index is present, so the
+        result can be saved by one rank and later loaded on a group of any size: :meth:`load_state_dict` keeps the
+        entries of the matrices the loading rank owns.  Matrices that have not been stepped yet have no entry.
         """
-        full: dict[int, torch.Tensor] = {}
+        sd = self.state_dict()
+        sd["owners"] = list(self.owners)
         if self.world == 1:
-            full = {i: st["momentum_buffer"] for i, st in self.state.items()}
-            return {"owners": list(self.owners), "momentum_buffer": full}
+            return sd
         # Which matrices have state is the same question on every rank only if the owners answer it.
         has = torch.zeros(len(self.params), dtype=torch.int32, device=self.params[0].device if self.params else "cpu")
-        for i in self.state:
-            has[i] = 1
+        for i, p in enumerate(self.params):
+            if "momentum_buffer" in self.state.get(p, {}):
+                has[i] = 1
         dist.all_reduce(has, op=dist.ReduceOp.MAX, group=self.group)
+        full: dict[int, dict[str, torch.Tensor]] = {}
         for i in has.nonzero().flatten().tolist():
             p, owner = self.params[i], self.owners[i]
-            buf = self.state[i]["momentum_buffer"] if owner == self.rank else torch.empty_like(p.data)
+            buf = self.state[p]["momentum_buffer"] if owner == self.rank else torch.empty_like(p.data)
             dist.broadcast(buf, src=dist.get_global_rank(self.group, owner) if self.group is not None else owner,
-                           group=self.group)
-            full[i] = buf
-        return {"owners": list(self.owners), "momentum_buffer": full}
+                           group=self.group)  # fmt: skip
+            full[i] = {"momentum_buffer": buf}
+        sd["state"] = full
+        return sd
 
-    def load_state_dict(self, sd: dict) -> None:
-        """Take (copies of) the momentum buffers of the matrices this rank owns; other entries are ignored."""
-        for i, buf in sd["momentum_buffer"].items():
-            if self.owners[int(i)] == self.rank:
-                self.state.setdefault(int(i), {})["momentum_buffer"] = buf.to(self.params[int(i)].device, copy=True)
+    def load_state_dict(self, state_dict: dict) -> None:  # type: ignore[override]
+        """Load a checkpoint written by ``state_dict()`` or :meth:`gathered_state_dict`; of the per-parameter
+        entries, only those of the matrices this rank owns are kept (as copies)."""
+        mine = {
+            int(i): {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in st.items()}
+            for i, st in state_dict["state"].items()
+            if self.owners[int(i)] == self.rank
+        }
+        super().load_state_dict({"state": mine, "param_groups": state_dict["param_groups"]})

@@ -135,7 +135,7 @@ def _worker_lp(rank, port, out, kw, exchange="updates"):
         opt.step()
     sd = opt.state_dict()
     full = opt.gathered_state_dict()
-    full_momentum = {i: b.numpy().copy() for i, b in full["momentum_buffer"].items()}  # owned entries alias the state
+    full_momentum = {i: st["momentum_buffer"].numpy().copy() for i, st in full["state"].items()}  # owned entries alias the state
     # A fresh optimizer that loads the gathered checkpoint keeps exactly the entries it owns, and continues
     # identically.
     params2 = [torch.nn.Parameter(p.detach().clone()) for p in params]
@@ -149,9 +149,9 @@ def _worker_lp(rank, port, out, kw, exchange="updates"):
         "params": [p.detach().numpy().copy() for p in params],
         "params_resumed": [p.detach().numpy().copy() for p in params2],
         "owned": opt.owned_indices(),
-        "state_keys": sorted(sd["momentum_buffer"]),
+        "state_keys": sorted(sd["state"]),
         "full_momentum": full_momentum,
-        "resumed_keys": sorted(opt2.state),
+        "resumed_keys": sorted(i for i, p in enumerate(params2) if "momentum_buffer" in opt2.state.get(p, {})),
         "n_buckets": len(opt.buckets),
     }
     dist.destroy_process_group()
@@ -228,3 +228,40 @@ def test_layer_parallel_rejects_non_2d():
         LayerParallelMuon([torch.nn.Parameter(torch.zeros(4))])
     with pytest.raises(ValueError, match="num_ns_steps must be at least 1"):
         LayerParallelMuon([torch.nn.Parameter(torch.zeros(4, 4))], num_ns_steps=0)
+
+
+def test_layer_parallel_is_a_torch_optimizer_with_parameter_groups(monkeypatch):
+    """Parameter groups with their own lr / weight decay, an LR scheduler, ``zero_grad`` and torch's own
+    ``state_dict`` layout (``momentum_buffer`` per parameter, as the single-process class keeps it) all work, and a
+    single-rank run equals Muon built from the same groups bit for bit."""
+    monkeypatch.setattr(muon_utils, "newton_schulz", _cpu_ns)
+    kw = dict(momentum=0.9, nesterov=True, num_ns_steps=5, coefficient_type="simple", scale_mode="shape_scaling")
+
+    def groups(ps):
+        return [{"params": ps[:3], "lr": 0.02, "weight_decay": 0.1}, {"params": ps[3:], "lr": 0.005, "weight_decay": 0.0}]
+
+    a, b = _make_params(), _make_params()
+    ref = Muon(groups(a), **kw)
+    lp = LayerParallelMuon(groups(b), bucket_numel=1024, **kw)
+    assert isinstance(lp, torch.optim.Optimizer)
+    assert [g["lr"] for g in lp.param_groups] == [0.02, 0.005]
+    sched = [torch.optim.lr_scheduler.StepLR(o, step_size=1, gamma=0.5) for o in (ref, lp)]
+    for step in range(3):
+        for ps in (a, b):
+            for p, g in zip(ps, _grads(step)):
+                p.grad = g.clone()
+        ref.step()
+        lp.step()
+        for s in sched:
+            s.step()
+    assert lp.param_groups[0]["lr"] == pytest.approx(0.02 * 0.125)
+    for pa, pb in zip(a, b):
+        assert torch.equal(pa, pb)
+        assert set(lp.state[pb]) == {"momentum_buffer"}
+        assert torch.equal(lp.state[pb]["momentum_buffer"], ref.state[pa]["momentum_buffer"])
+    sd = lp.state_dict()
+    assert sorted(sd["state"]) == list(range(len(SHAPES))) and len(sd["param_groups"]) == 2
+    lp.zero_grad()
+    assert all(p.grad is None for p in b)
+    with pytest.raises(ValueError, match="closure is not supported"):
+        lp.step(lambda: 0.0)

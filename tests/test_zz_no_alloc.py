@@ -6,8 +6,8 @@ raw device pointers from another runtime.  For them the partial sums live in an 
 This test calls that entry point through the C ABI twice in a row, on inputs of different sizes so that the second
 call finds the first call's leftovers in the shared array, and requires the same bits as ``eo_sumsq_f32``
 (both run the same kernels in the same order; the tolerance used elsewhere for this quantity, rtol 1e-12, is
-therefore met with equality).  It is collected last so that a stop-at-first-failure run has already covered
-everything else.
+therefore met with equality).  The file name sorts after every other test file, so these cases are collected
+and run last.
 """
 
 
