@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE config 4 on one device): a "step" is one full ``newton_schulz`` call -- Frobenius
+Headline workload (BASELINE config 4 on one device): a "step" is one full ``newton_schulz`` call -- Frobenius
 normalisation, bf16 down-cast, five "simple" iterations (A = XX^T, B = bA + cA^2, X <- aX + BX) on the sm_100a
 kernels and the fp32 result -- on one 8192 x 28672 fp32 matrix.  With N > 1 every rank orthogonalizes its own
 matrix of that shape (layer-parallel partitioning: the matrices of a model are independent units) and the ranks
@@ -14,13 +14,20 @@ SYRK benchmark, which credits a symmetric product like a general one) summed ove
 object credits symmetric outputs once (what the kernels actually execute) and compares with the measured
 cuBLAS bf16 peak of this GPU pool.
 
-``--impl reference`` times the CPU restatement of the reference (oracle/ns_oracle.py, numpy + OpenBLAS on all
-host cores) on a bounded corner block of the same matrix.
+The same JSON line carries, as further objects, the other configurations the metric names, each with its parity
+check: ``muon_step`` (config 3: one Muon step over a Llama-3-8B-shaped parameter set, layer-parallel over the N
+ranks), ``tp_ns`` (config 4 sharded: tensor-parallel Newton-Schulz over the N ranks, N > 1), ``per_head``
+(config 5: 6400 per-head matrices divided among the ranks), ``syrk_config2`` (config 2: the batched SYRK) and
+``gpu_library_baseline`` (the reference's GPU arithmetic, cuBLAS through torch, timed in the same run).
+
+``--impl reference`` times the CPU restatement of the reference (oracle/ns_torch_cpu.py: the reference's own torch
+CPU operators on all host cores) on a bounded corner block of the same matrix.
 """
 
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -33,10 +40,16 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 M, N_COLS, NS_STEPS, COEFF = 8192, 28672, 5, "simple"
+ABC = (3.4445, -4.7750, 2.0315)  # the "simple" tuple
 CPU_SAMPLE = (2048, 7168)  # corner block timed on the host
 NOMINAL_BF16_TFLOPS = 2250.0
 TRAFFIC_BYTES_PER_LAUNCH = 0.67e9
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+LAYER_SHAPES = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336)]
+MUON_KW = dict(lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True, weight_decay_method="decoupled",
+               num_ns_steps=NS_STEPS, scale_mode="shape_scaling", coefficient_type=COEFF, fp32_matmul_prec="medium",
+               use_syrk=True)  # fmt: skip
+HEADS_TOTAL, HEAD_SHAPE, HEAD_CHUNK = 6400, (128, 8192), 800
 
 
 def flops(m: int, n: int, steps: int) -> tuple[float, float]:
@@ -55,28 +68,44 @@ def load_peaks() -> tuple[dict, str]:
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
-def cpu_reference(steps: int, warmup: int) -> dict:
-    """Time the numpy restatement of the reference on the host cores; returns the cpu_baseline object."""
-    import numpy as np
-
-    from oracle import ns_oracle
+def use_all_host_cores() -> int:
+    """Let torch's CPU operators (and any BLAS behind numpy) use every core this process may run on, whatever
+    OMP_NUM_THREADS the launcher exported (torch.distributed.run sets it to 1).  Returns the thread count."""
+    import torch
 
     try:
-        from threadpoolctl import threadpool_info
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    try:
+        from threadpoolctl import threadpool_limits
 
-        cores = max([p.get("num_threads", 1) for p in threadpool_info()] or [os.cpu_count() or 1])
+        threadpool_limits(limits=n)
     except Exception:
-        cores = os.cpu_count() or 1
+        pass
+    return torch.get_num_threads()
+
+
+def cpu_reference(steps: int, warmup: int) -> dict:
+    """Time the torch-CPU restatement of the reference on the host cores; returns the cpu_baseline object."""
+    import torch
+
+    from oracle import ns_torch_cpu
+
+    cores = use_all_host_cores()
     m, n = CPU_SAMPLE
-    rng = np.random.default_rng(3)
-    x = rng.standard_normal((m, n), dtype=np.float32)
-    for _ in range(max(warmup, 0)):
-        ns_oracle.newton_schulz(x, 1, COEFF, precision="medium")
+    g = torch.Generator(device="cpu").manual_seed(3)
+    x = torch.randn(m, n, generator=g, dtype=torch.float32)
+    for _ in range(max(warmup, 1)):
+        ns_torch_cpu.newton_schulz(x, 1, COEFF, "medium")
     times = []
     for _ in range(max(steps, 1)):
         t0 = time.perf_counter()
-        ns_oracle.newton_schulz(x, NS_STEPS, COEFF, precision="medium")
+        ns_torch_cpu.newton_schulz(x, NS_STEPS, COEFF, "medium")
         times.append(time.perf_counter() - t0)
+        if sum(times) > 25.0:
+            break
     dense, _ = flops(m, n, NS_STEPS)
     total = sum(times)
     return {
@@ -84,8 +113,9 @@ def cpu_reference(steps: int, warmup: int) -> dict:
         "unit": "TFLOP/s",
         "cores": int(cores),
         "kind": "port",
-        "sample": f"{len(times)} x newton_schulz({m}x{n} corner block, {NS_STEPS} '{COEFF}' steps, bf16-rounded "
-        f"operands, fp32 accumulate) in numpy/OpenBLAS; {total / len(times):.2f} s per call",
+        "sample": f"{len(times)} x newton_schulz({m}x{n} corner block of the {M}x{N_COLS} workload, {NS_STEPS} "
+        f"'{COEFF}' steps) with the reference's own CPU operators (torch bf16 matmul / addmm at precision 'medium', "
+        f"{cores} threads); {total / len(times):.2f} s per call",
         "ms_per_step": 1e3 * total / len(times),
     }
 
@@ -97,6 +127,8 @@ def run_reference_arm(args) -> None:
     # Keep the whole run within a few minutes whatever K is.
     steps = max(1, min(args.steps, 20))
     base = cpu_reference(steps, min(args.warmup, 2))
+    cfg = workload_config(args.gpus)
+    cfg["timed_on_host"] = f"{CPU_SAMPLE[0]}x{CPU_SAMPLE[1]} corner block per step (bounded sample), kind: port"
     line = {
         "impl": "reference",
         "metric": "newton_schulz_tflops",
@@ -111,7 +143,7 @@ def run_reference_arm(args) -> None:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": cfg,
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -192,7 +224,118 @@ class ClockSampler:
         return out
 
 
-def run_gpu_arm(args) -> None:
+def bind_host_to_gpu(local_rank: int) -> str:
+    """Pin this process to the CPU cores next to its GPU (NVML's affinity mask), so that pinned host buffers are
+    allocated on that NUMA node and host <-> device copies of different ranks do not share one socket's memory.
+    Returns a description for the config object; does nothing if NVML or the affinity call is not available."""
+    try:
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(local_rank).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        allowed = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (max(allowed) + 64) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        cpus = near & allowed
+        if cpus and cpus != allowed:
+            os.sched_setaffinity(0, cpus)
+            return f"bound to {len(cpus)} cores near the GPU"
+        return "all allowed cores are near the GPU"
+    except Exception as exc:  # noqa: BLE001
+        return f"not bound ({type(exc).__name__})"
+
+
+class Ctx:
+    """Process-group context of one bench process."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={self.world}: launch with torch.distributed.run "
+                             f"--nproc-per-node {args.gpus}")  # fmt: skip
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.binding = bind_host_to_gpu(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=300))
+        self.group = dist.group.WORLD if self.world > 1 else None
+
+    def barrier(self) -> None:
+        import torch
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, *vals: float) -> list[float]:
+        import torch
+        import torch.distributed as dist
+
+        t = torch.tensor(list(vals), device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t]
+
+    def close(self) -> None:
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+
+
+def timed(fn, warm: int, steps: int) -> float:
+    """Mean milliseconds of ``fn()`` over ``steps`` calls after ``warm`` calls, CUDA events on the current stream."""
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def rel_fro(a, b) -> float:
+    return float((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-300))
+
+
+def library_newton_schulz(x, steps: int = NS_STEPS, abc=ABC):
+    """The reference's GPU arithmetic for one call (muon_utils.py:216, 262-269, 370-377 there): Frobenius
+    normalisation, bf16 cast, ``steps`` iterations of three library (cuBLAS) products, fp32 result.  ``x`` is fp32,
+    2-D or batched 3-D; tall inputs are iterated in the wide orientation."""
+    import torch
+
+    tall = x.size(-2) > x.size(-1)
+    if tall:
+        x = x.mT
+    X = (x / x.norm(dim=(-2, -1), keepdim=True).clamp_min(1e-15)).to(torch.bfloat16)
+    a, b, c = abc
+    for _ in range(steps):
+        A = X @ X.mT
+        if X.ndim == 3:
+            B = torch.baddbmm(A, A, A, alpha=c, beta=b)
+            X = torch.baddbmm(X, B, X, alpha=1.0, beta=a)
+        else:
+            B = torch.addmm(A, A, A, alpha=c, beta=b)
+            X = torch.addmm(X, B, X, alpha=1.0, beta=a)
+    X = X.to(torch.float32)
+    return X.mT if tall else X
+
+
+def headline_section(ctx: Ctx, args) -> dict:
     import torch
     import torch.distributed as dist
 
@@ -200,21 +343,7 @@ def run_gpu_arm(args) -> None:
     from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
     from emerging_optimizers_b200.utils import fp32_matmul_precision
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    def barrier() -> None:
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     g = torch.Generator(device="cpu").manual_seed(3 + rank)
     x_host = torch.empty(M, N_COLS, dtype=torch.float32).pin_memory()
     # Same distribution as config 4 (N(0,1)); generated in row blocks to bound host memory traffic.
@@ -274,48 +403,41 @@ def run_gpu_arm(args) -> None:
     for _ in range(n_warm):
         step_device()
     side.synchronize()
-    barrier()
+    ctx.barrier()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(ctx.local_rank)
     if rank == 0 and not args.kernels_only:
         sampler.start()
         time.sleep(0.3)
 
     # ---- timed region 1: inputs resident in HBM -------------------------------------------------
+    # The last few steps are also bracketed per library call (CUDA events on the launching stream around the 15
+    # tensor-core launches of one newton_schulz call), so that the roofline figure is taken inside the sustained
+    # loop, under the same clocks as ms_per_step.
+    n_bracketed = 0 if args.kernels_only else min(5, args.steps)
     launches0 = _native.launch_count
-    barrier()
+    ctx.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        if n_bracketed and i == args.steps - n_bracketed:
+            _native.launch_timer = []
         step_device()
     torch.cuda.current_stream().wait_stream(side)
     e1.record()
-    barrier()
+    ctx.barrier()
     ms_total = e0.elapsed_time(e1)
     launches = _native.launch_count - launches0
+    timer, _native.launch_timer = (_native.launch_timer or []), None
     clocks = sampler.stop() if rank == 0 else {}
     if args.kernels_only:
-        if rank == 0:
-            dense, sym = flops(M, N_COLS, NS_STEPS)
-            nb = max(args.batch, 1)
-            print(json.dumps({"kernels_only": True, "shape": [M, N_COLS], "batch": args.batch,
-                              "ms_per_step": ms_total / args.steps,
-                              "tflops_dense_eq": nb * dense * args.steps / (ms_total / 1e3) / 1e12,
-                              "gpu_launches": launches, "device_status": _native.read_device_status(dev)}), flush=True)
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
-        return
-
-    # ---- per-launch timing of the tensor-core kernel (same stream, CUDA events around each launch) ----
-    _native.launch_timer = []
-    for _ in range(2):
-        ns_call(x)
-    torch.cuda.synchronize()
-    kernel_ms = [a.elapsed_time(b) for _, a, b, _ in _native.launch_timer]
-    names = [n for n, _, _, _ in _native.launch_timer]
-    kernel_launches = sum(k for _, _, _, k in _native.launch_timer)
-    _native.launch_timer = None
+        dense, sym = flops(M, N_COLS, NS_STEPS)
+        nb = max(args.batch, 1)
+        return {"kernels_only": True, "shape": [M, N_COLS], "batch": args.batch, "ms_per_step": ms_total / args.steps,
+                "tflops_dense_eq": nb * dense * args.steps / (ms_total / 1e3) / 1e12, "gpu_launches": launches,
+                "device_status": _native.read_device_status(dev)}  # fmt: skip
+    call_ms = [a.elapsed_time(b) for _, a, b, _ in timer]
+    kernel_launches = sum(k for _, _, _, k in timer)
 
     # ---- timed region 2: end to end with host buffers ------------------------------------------
     # Pinned fp32 input -> device, newton_schulz, fp32 result -> pinned host, every step; the three stages of
@@ -323,8 +445,7 @@ def run_gpu_arm(args) -> None:
     y_host = torch.empty(M, N_COLS, dtype=torch.float32).pin_memory()
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
     bufs = [torch.empty_like(x) for _ in range(2)]
-    free_in = [None, None]   # event: compute that read bufs[i] has finished
-    outs = [None, None]
+    free_in = [None, None]  # event: compute that read bufs[i] has finished
 
     def e2e_loop(k: int) -> None:
         cur = torch.cuda.current_stream()
@@ -345,245 +466,398 @@ def run_gpu_arm(args) -> None:
                 s_out.wait_event(done)
                 y_host.copy_(y, non_blocking=True)
                 y.record_stream(s_out)
-            outs[b] = y
         cur.wait_stream(s_out)
 
     e2e_loop(2)
-    barrier()
+    ctx.barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     e2e_loop(args.steps)
     f1.record()
-    barrier()
+    ctx.barrier()
     ms_e2e = f0.elapsed_time(f1)
-
     status = _native.read_device_status(dev)
+    ms_total, ms_e2e = ctx.max_over_ranks(ms_total, ms_e2e)
+    del bufs, peer, gather_buf
+    torch.cuda.empty_cache()
 
-    # ---- reduce over ranks ------------------------------------------------------------------------
-    t = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = float(t[0]), float(t[1])
-
-    if rank == 0:
-        dense, sym = flops(M, N_COLS, NS_STEPS)
-        peaks, peak_kind = load_peaks()
-        sec = ms_total / 1e3
-        value = dense * args.steps * world / sec / 1e12
-        # The timed region is seconds long, so the sustained cuBLAS figure is the denominator.
-        peak = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
-        k_total_ms = sum(kernel_ms)
-        n_launch = kernel_launches
-        # two newton_schulz calls were timed: 2 * sym FLOP in n_launch launches of eo_gemm_kernel
-        achieved = (sym * 2 / n_launch) / (k_total_ms / n_launch / 1e3) / 1e12 if n_launch else None
-        by_name = {}
-        for nme, ms in zip(names, kernel_ms):
-            by_name.setdefault(nme, []).append(ms)
-        cpu = cpu_reference(4, 1) if world == 1 else None
-        line = {
-            "metric": "newton_schulz_tflops",
-            "value": value,
+    dense, sym = flops(M, N_COLS, NS_STEPS)
+    peaks, peak_kind = load_peaks()
+    sec = ms_total / 1e3
+    sustained = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
+    burst = float(peaks["bf16_tflops"])
+    mean_call = sum(call_ms) / len(call_ms) if call_ms else None
+    achieved = sym / (mean_call / 1e3) / 1e12 if mean_call else None
+    per_call_launches = kernel_launches // max(len(call_ms), 1)
+    line = {
+        "metric": "newton_schulz_tflops",
+        "value": dense * args.steps * world / sec / 1e12,
+        "unit": "TFLOP/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": n_warm,
+        "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic",
+        "config": dict(workload_config(world), host_binding=ctx.binding),
+        "tflops_sym": sym * args.steps * world / sec / 1e12,
+        "pct_of_measured_peak_sym": 100.0 * sym * args.steps / sec / 1e12 / sustained,
+        "pct_of_nominal_peak_sym": 100.0 * sym * args.steps / sec / 1e12 / NOMINAL_BF16_TFLOPS,
+        "roofline": {
+            "bound": "tensor",
+            "kernel": "eo_gemm_kernel (the Gram SYRK, A^2 SYRK and BX GEMM launches of one newton_schulz call)",
+            "achieved": achieved,
+            "peak": sustained,
+            "peak_kind": f"bf16_tflops_sustained ({peak_kind}): the launches are timed inside the seconds-long loop",
             "unit": "TFLOP/s",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": n_warm,
-            "ms_per_step": ms_total / args.steps,
-            "higher_is_better": True,
-            "scaling": "weak",
-            "vs_baseline": None,
-            "dtype": "bf16",
-            "data": "synthetic",
-            "config": workload_config(world),
-            "tflops_sym": sym * args.steps * world / sec / 1e12,
-            "pct_of_measured_peak_sym": 100.0 * sym * args.steps / sec / 1e12 / peak,
-            "pct_of_nominal_peak_sym": 100.0 * sym * args.steps / sec / 1e12 / NOMINAL_BF16_TFLOPS,
-            "roofline": {
-                "bound": "tensor",
-                "kernel": "eo_gemm_kernel (Gram SYRK, A^2 SYRK and BX GEMM launches of one call, averaged)",
-                "achieved": achieved,
-                "peak": peak,
-                "peak_kind": f"bf16_tflops_sustained, {peak_kind}",
-                "unit": "TFLOP/s",
-                "frac": (achieved / peak) if achieved else None,
-                "frac_of_burst_peak": (achieved / float(peaks["bf16_tflops"])) if achieved else None,
-                # DRAM bytes per launch: read + write of the Gram, A^2 and BX launches of one iteration measured by
-                # ncu on 4096 x 16384 (138 + 35 + 398 MB), scaled by operand bytes to this shape and averaged over
-                # the three launches.
-                "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
-                "algorithmic_flops_per_launch": sym * 2 / n_launch if n_launch else None,
-                "avg_launch_ms": k_total_ms / n_launch if n_launch else None,
-                "call_ms": {k: sum(v) / len(v) for k, v in by_name.items()},
-                "launches_timed": n_launch,
-            },
-            "e2e": {
-                "value": dense * args.steps * world / (ms_e2e / 1e3) / 1e12,
-                "unit": "TFLOP/s",
-                "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": x_host.numel() * 4 * world,
-                "d2h_bytes_per_step": y_host.numel() * 4 * world,
-            },
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "device_status": status,
-        }
-        if cpu is not None:
-            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
-
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+            "frac": (achieved / sustained) if achieved else None,
+            "frac_of_burst_peak": (achieved / burst) if achieved else None,
+            # DRAM bytes per launch: read + write of the Gram, A^2 and BX launches of one iteration measured by
+            # ncu on 4096 x 16384 (138 + 35 + 398 MB), scaled by operand bytes to this shape and averaged over
+            # the three launches.
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
+            "algorithmic_flops_per_launch": sym / per_call_launches if per_call_launches else None,
+            "avg_launch_ms": mean_call / per_call_launches if mean_call and per_call_launches else None,
+            "call_ms": mean_call,
+            "calls_timed": len(call_ms),
+            "launches_per_call": per_call_launches,
+            "timed_where": "CUDA events around the tensor-core launches of the last calls of the timed loop",
+            "call_ms_x_sm_mhz": (mean_call * clocks["sm_mhz"]) if mean_call and clocks.get("sm_mhz") else None,
+        },
+        "e2e": {
+            "value": dense * args.steps * world / (ms_e2e / 1e3) / 1e12,
+            "unit": "TFLOP/s",
+            "ms_per_step": ms_e2e / args.steps,
+            "h2d_bytes_per_step": x_host.numel() * 4 * world,
+            "d2h_bytes_per_step": y_host.numel() * 4 * world,
+        },
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "device_status": status,
+    }
+    return line
 
 
-def run_muon_step(args) -> None:
-    """Secondary workload (BASELINE config 3): one Muon step over a Llama-3-8B-shaped parameter set, 32 layers of
-    q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336; fp32 params, bf16-rounded N(0, 1e-3)
-    gradients, Nesterov momentum 0.95, lr 0.02, decoupled weight decay 0.1, shape_scaling, five "simple" steps.
-    On N > 1 GPUs the matrices are divided among the ranks (layer-parallel) and the bf16 updates all-gathered;
-    total work is fixed, so scaling is "strong"."""
+def library_section(ctx: Ctx) -> tuple[dict, dict]:
+    """The reference's GPU arithmetic (torch / cuBLAS) timed beside the kernels, same device, same run: the
+    headline call, and config 2 (batched SYRK 32 x 2048 x 8192 against torch.bmm, TF-eq = 2 B N^2 K / t as in the
+    reference's benchmarks/bench_batched_syrk.py:89)."""
+    import torch
+
+    from emerging_optimizers_b200 import triton_kernels as tk
+    from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+    from emerging_optimizers_b200.utils import fp32_matmul_precision
+
+    dev = ctx.dev
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(M, N_COLS, generator=g, device=dev)
+    lib_ms = timed(lambda: library_newton_schulz(x), 2, 5)
+
+    def ours():
+        with fp32_matmul_precision("medium"):
+            return muon_utils.newton_schulz(x, NS_STEPS, COEFF, use_syrk=True)
+
+    our_ms = timed(ours, 2, 5)
+    err = rel_fro(ours(), library_newton_schulz(x))
+    dense, _ = flops(M, N_COLS, NS_STEPS)
+    lib_ms, our_ms = ctx.max_over_ranks(lib_ms, our_ms)
+    base = {
+        "what": f"newton_schulz {M}x{N_COLS}, {NS_STEPS} '{COEFF}' steps with torch / cuBLAS bf16 products (the "
+        "reference's GPU arithmetic), device-resident, 5 calls back to back",
+        "ms_per_step": lib_ms,
+        "tflops_dense_eq": dense / (lib_ms / 1e3) / 1e12,
+        "this_library_ms_same_loop": our_ms,
+        "speedup": lib_ms / our_ms,
+        "rel_fro_this_library_vs_library_gemm": err,
+    }
+    del x
+    B, N, K = 32, 2048, 8192
+    g = torch.Generator(device=dev).manual_seed(1)
+    xs = (torch.randn(B, N, K, generator=g, device=dev) / K**0.5).to(torch.bfloat16)
+    syrk_ms = timed(lambda: tk.batched_tsyrk_ex(xs), 5, 20)
+    bmm_ms = timed(lambda: torch.bmm(xs, xs.mT), 5, 20)
+    a = tk.batched_tsyrk_ex(xs)
+    want = torch.bmm(xs.float(), xs.float().mT)
+    tf = 2.0 * B * N * N * K / 1e12
+    syrk_ms, bmm_ms = ctx.max_over_ranks(syrk_ms, bmm_ms)
+    cfg2 = {
+        "what": f"batched SYRK {B} x {N} x {K} bf16, entries N(0, 1/{K}), seed 1; TF-eq = 2 B N^2 K / t",
+        "ms": syrk_ms,
+        "tf_eq": tf / (syrk_ms / 1e3),
+        "torch_bmm_ms": bmm_ms,
+        "torch_bmm_tf_eq": tf / (bmm_ms / 1e3),
+        "speedup": bmm_ms / syrk_ms,
+        "rel_fro_vs_fp32_accumulated": rel_fro(a, want),
+        "max_rel_err": float(((a.float() - want).abs() / want.abs().clamp_min(1e-2)).max()),
+        "exactly_symmetric": bool(torch.equal(a, a.mT)),
+    }
+    return base, cfg2
+
+
+def muon_step_section(ctx: Ctx, args) -> dict:
+    """BASELINE config 3: one Muon step over a Llama-3-8B-shaped parameter set (32 layers of q/o 4096x4096, k/v
+    1024x4096, gate/up 14336x4096, down 4096x14336; fp32 params N(0, 0.02^2), bf16-rounded N(0, 1e-6) gradients,
+    Nesterov momentum 0.95, lr 0.02, decoupled weight decay 0.1, shape_scaling, five "simple" steps), divided
+    among the N ranks by LayerParallelMuon.  Total work is fixed ("strong" scaling).  Checked in the same run
+    against the single-process step (every rank also runs the whole step alone: its time is ``n1_ms_same_run``,
+    its parameters after three steps the reference for ``rel_fro_vs_single_process``) and, for the first step of a
+    subset of matrices, against the step restated with library GEMMs."""
     import torch
     import torch.distributed as dist
 
     from emerging_optimizers_b200 import _native
     from emerging_optimizers_b200.distributed import LayerParallelMuon
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     layers = args.layers
-    layer = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336)]
-    g = torch.Generator(device=dev).manual_seed(2)
-    params = []
-    for _ in range(layers):
-        for s in layer:
-            p = torch.nn.Parameter(torch.randn(*s, generator=g, device=dev) * 0.02)
-            p.grad = (torch.randn(*s, generator=g, device=dev) * 1e-3).bfloat16().float()
-            params.append(p)
-    opt = LayerParallelMuon(params, lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True,
-                            weight_decay_method="decoupled", num_ns_steps=5, scale_mode="shape_scaling",
-                            coefficient_type="simple", fp32_matmul_prec="medium", use_syrk=True,
-                            exchange=args.lp_exchange,
-                            **({"bucket_numel": args.bucket_numel} if args.bucket_numel else {}))  # fmt: skip
+    shapes = LAYER_SHAPES * layers
+    subset = sorted(set(list(range(len(LAYER_SHAPES))) + list(range(len(shapes) - len(LAYER_SHAPES), len(shapes)))))
+    parity_steps = 3
 
-    def barrier() -> None:
-        if world > 1:
-            dist.barrier()
+    def fill(tensors, seed, scale, bf16_round):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        for t in tensors:
+            v = torch.randn(t.shape, generator=gen, device=dev) * scale
+            t.copy_(v.bfloat16().float() if bf16_round else v)
+
+    params = [torch.nn.Parameter(torch.empty(s, device=dev)) for s in shapes]
+    grads = [torch.empty(s, device=dev) for s in shapes]
+    with torch.no_grad():
+        fill([p.data for p in params], 3, 0.02, False)
+        fill(grads, 2, 1e-3, True)
+    for p, g in zip(params, grads):
+        p.grad = g
+    p0 = {i: params[i].detach().clone() for i in subset}
+
+    def library_first_step(i: int) -> torch.Tensor:
+        """Parameter i after the first step, restated with torch operators and library GEMMs
+        (orthogonalized_optimizer.py:164-212 and muon.py:117-132 of the reference)."""
+        kw = MUON_KW
+        p, g = p0[i].clone(), grads[i]
+        p.add_(p, alpha=-kw["weight_decay"] * kw["lr"])
+        m = torch.zeros_like(g).lerp_(g, 1 - kw["momentum"])
+        u = g.lerp(m, kw["momentum"])
+        o = library_newton_schulz(u)
+        scale = max(1, p.size(0) / p.size(1)) ** 0.5
+        return p.add_(o * scale * 1.0, alpha=-kw["lr"])
+
+    out: dict = {}
+    solo_params_after = None
+    if world > 1:
+        # single-process step on every rank at once (a group of one rank each), for time and for parity
+        solo = None
+        for r in range(world):
+            grp = dist.new_group([r])
+            if r == rank:
+                solo = grp
+        opt1 = LayerParallelMuon(params, group=solo, **MUON_KW)
+        ctx.barrier()
+        opt1.step()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(parity_steps - 1):
+            opt1.step()
+        e1.record()
         torch.cuda.synchronize()
+        out["n1_ms_same_run"] = ctx.max_over_ranks(e0.elapsed_time(e1) / (parity_steps - 1))[0]
+        solo_params_after = {i: params[i].detach().clone() for i in subset}
+        del opt1
+        torch.cuda.empty_cache()
+        with torch.no_grad():
+            fill([p.data for p in params], 3, 0.02, False)
 
-    for _ in range(max(args.warmup, 1)):
+    opt = LayerParallelMuon(params, group=ctx.group, exchange=args.lp_exchange,
+                            **({"bucket_numel": args.bucket_numel} if args.bucket_numel else {}), **MUON_KW)  # fmt: skip
+    opt.step()
+    torch.cuda.synchronize()
+    errs = [rel_fro(params[i].detach() - p0[i], library_first_step(i) - p0[i]) for i in subset[: len(LAYER_SHAPES)]]
+    out["rel_fro_update_step1_vs_library_gemm"] = ctx.max_over_ranks(max(errs))[0]
+    for _ in range(parity_steps - 1):
         opt.step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    torch.cuda.synchronize()
+    if solo_params_after is not None:
+        worst = max(rel_fro(params[i].detach(), solo_params_after[i]) for i in subset)
+        same = all(torch.equal(params[i].detach(), solo_params_after[i]) for i in subset)
+        out["rel_fro_vs_single_process"] = ctx.max_over_ranks(worst)[0]
+        out["bitwise_equal_to_single_process"] = bool(ctx.max_over_ranks(0.0 if same else 1.0)[0] == 0.0)
+        del solo_params_after
+    out["parity_subset"] = f"the {len(subset)} matrices of the first and the last layer, after {parity_steps} steps"
+
+    ctx.barrier()
     launches0 = _native.launch_count
+    k = max(2, min(args.muon_steps, 20))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    ctx.barrier()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(k):
         opt.step()
     e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    clocks = sampler.stop() if rank == 0 else {}
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ctx.barrier()
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1) / k)[0]
     # checksum over ranks: parameters must be identical everywhere
-    chk = torch.stack([p.detach().double().sum() for p in params[:: max(1, len(params) // 16)]]).sum().reshape(1)
+    chk = torch.stack([p.detach().double().sum() for p in params[:: max(1, len(params) // 32)]])
     same = True
     if world > 1:
         lo, hi = chk.clone(), chk.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         same = bool((lo == hi).all())
-    status = _native.read_device_status(dev)
-    if rank == 0:
-        dense = layers * sum(flops(min(s), max(s), NS_STEPS)[0] for s in layer)
-        sym = layers * sum(flops(min(s), max(s), NS_STEPS)[1] for s in layer)
-        print(json.dumps({
-            "metric": "muon_step_ms", "value": float(t[0]), "unit": "ms", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 1), "ms_per_step": float(t[0]), "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"Muon step, Llama-3-8B-shaped parameter set ({layers} layers, {len(params)} matrices, "
-                       f"{sum(p.numel() for p in params) / 1e9:.2f} G parameters), layer-parallel x{world}",
-                       "exchange": args.lp_exchange, "l2": "parameter set far larger than L2"},
-            "tflops_dense_eq": dense / (float(t[0]) / 1e3) / 1e12, "tflops_sym": sym / (float(t[0]) / 1e3) / 1e12,
-            "params_identical_across_ranks": same, "gpu_launches": (_native.launch_count - launches0),
-            "clocks": clocks, "device_status": status,
-        }), flush=True)  # fmt: skip
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    dense = layers * sum(flops(min(s), max(s), NS_STEPS)[0] for s in LAYER_SHAPES)
+    sym = layers * sum(flops(min(s), max(s), NS_STEPS)[1] for s in LAYER_SHAPES)
+    out.update({
+        "what": f"Muon step, Llama-3-8B-shaped parameter set ({layers} layers, {len(params)} matrices, "
+        f"{sum(p.numel() for p in params) / 1e9:.2f} G parameters), layer-parallel x{world}, exchange of "
+        f"{args.lp_exchange}; strong scaling",
+        "ms": ms, "steps_timed": k, "warmup_steps": parity_steps,
+        "tflops_dense_eq": dense / (ms / 1e3) / 1e12, "tflops_sym": sym / (ms / 1e3) / 1e12,
+        "params_identical_across_ranks": same, "gpu_launches": _native.launch_count - launches0,
+        "device_status": _native.read_device_status(dev),
+    })  # fmt: skip
+    if "n1_ms_same_run" in out:
+        out["efficiency_vs_n1"] = out["n1_ms_same_run"] / (world * ms)
+    del opt, params, grads, p0
+    torch.cuda.empty_cache()
+    return out
 
 
-def run_tp_ns(args) -> None:
-    """Secondary workload (BASELINE config 4): tensor-parallel Newton-Schulz of one 8192 x 28672 matrix whose
-    columns are sharded over the N ranks; per iteration the partial Gram matrices are all-reduced (fused into the
-    SYRK epilogue, or NCCL with --exchange nccl).  Total work is fixed: "strong" scaling."""
+def tp_section(ctx: Ctx, args) -> dict:
+    """BASELINE config 4 sharded: tensor-parallel Newton-Schulz of one 8192 x 28672 matrix whose columns are sharded
+    over the N ranks; per iteration the partial Gram matrices are summed inside the SYRK kernel (fused) or by an
+    NCCL all-reduce behind it (nccl, timed for comparison).  Total work is fixed: "strong" scaling.  The gathered
+    result is compared with single-device Newton-Schulz on the gathered matrix."""
     import torch
     import torch.distributed as dist
+
+    from emerging_optimizers_b200 import _native
+    from emerging_optimizers_b200.distributed import tensor_parallel
+    from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
+    from emerging_optimizers_b200.utils import fp32_matmul_precision
+
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
+    cols = N_COLS // world
+    g = torch.Generator(device=dev).manual_seed(3 + rank)
+    x = torch.randn(M, cols, generator=g, device=dev)
+
+    def call(mode: str):
+        os.environ["EO_TP_GRAM"] = mode
+        with fp32_matmul_precision("medium"):
+            return muon_utils.newton_schulz_tp(x, NS_STEPS, COEFF, ctx.group, partition_dim=1, tp_mode="distributed",
+                                               use_syrk=True)  # fmt: skip
+
+    k = max(5, min(args.steps, 20))
+    res = {}
+    for mode in ("auto", "nccl"):
+        ctx.barrier()
+        res[mode] = ctx.max_over_ranks(timed(lambda: call(mode), 3, k))[0]
+    y_fused, y_nccl = call("auto"), call("nccl")
+    os.environ["EO_TP_GRAM"] = "auto"
+    shards = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(shards, x)
+    full = torch.cat(shards, dim=1)
+    del shards
+    with fp32_matmul_precision("medium"):
+        y_full = muon_utils.newton_schulz(full, NS_STEPS, COEFF, use_syrk=True)
+    mine = y_full[:, rank * cols : (rank + 1) * cols]
+    err_fused, err_nccl = ctx.max_over_ranks(rel_fro(y_fused, mine), rel_fro(y_nccl, mine))
+    ex = tensor_parallel._exchange(M, ctx.group, dev)
+    dense, _ = flops(M, N_COLS, NS_STEPS)
+    return {
+        "what": f"tensor-parallel newton_schulz {M}x{N_COLS}, column shards of {cols}, {NS_STEPS} '{COEFF}' steps; "
+        "strong scaling",
+        "ms": res["auto"],
+        "exchange": "SYRK + all-reduce in one kernel: "
+        + ("NVSwitch multimem load-reduce / multicast stores" if ex.multicast else "peer loads / stores")
+        + (", S in row blocks gathered by multicast stores" if world >= muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD else ""),
+        "ms_nccl_allreduce": res["nccl"],
+        "steps_timed": k,
+        "tflops_dense_eq": dense / (res["auto"] / 1e3) / 1e12,
+        "rel_fro_vs_single_device": err_fused,
+        "rel_fro_vs_single_device_nccl": err_nccl,
+        "device_status": _native.read_device_status(dev),
+    }
+
+
+def per_head_section(ctx: Ctx, args) -> dict:
+    """BASELINE config 5: 6400 per-head matrices of 128 x 8192 (a Llama-3-70B-shaped attention stack split per
+    head), divided among the N ranks (independent units, no collective), orthogonalized in chunks of 800 by the
+    fused small-matrix kernel.  One chunk of seeded data is reused for every chunk of a rank."""
+    import torch
 
     from emerging_optimizers_b200 import _native
     from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
     from emerging_optimizers_b200.utils import fp32_matmul_precision
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    os.environ["EO_TP_GRAM"] = "nccl" if args.exchange == "nccl" else "fused"
-    if args.tp_shard_poly_min_world:
-        muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD = args.tp_shard_poly_min_world
-    cols = N_COLS // world
-    g = torch.Generator(device=dev).manual_seed(3 + rank)
-    x = torch.randn(M, cols, generator=g, device=dev)
-    group = dist.group.WORLD if world > 1 else None
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
+    heads_here = HEADS_TOTAL // world
+    chunks = max(1, heads_here // HEAD_CHUNK)
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    x = (torch.randn(HEAD_CHUNK, *HEAD_SHAPE, generator=g, device=dev) * 1e-3).bfloat16().float()
 
-    def call():
+    def step():
         with fp32_matmul_precision("medium"):
-            if world == 1:
-                return muon_utils.newton_schulz(x, NS_STEPS, COEFF, use_syrk=True)
-            return muon_utils.newton_schulz_tp(x, NS_STEPS, COEFF, group, partition_dim=1, tp_mode="distributed",
-                                               use_syrk=True)  # fmt: skip
+            for _ in range(chunks):
+                y = muon_utils.newton_schulz(x, NS_STEPS, COEFF, use_syrk=True)
+        return y
 
-    for _ in range(max(args.warmup, 3)):
-        call()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        call()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    status = _native.read_device_status(dev)
-    if rank == 0:
-        dense, sym = flops(M, N_COLS, NS_STEPS)
-        ms = float(t[0])
-        print(json.dumps({
-            "metric": "tp_newton_schulz_ms", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"tensor-parallel newton_schulz {M}x{N_COLS}, column shards of {cols}, "
-                       f"{NS_STEPS} '{COEFF}' steps, Gram exchange: {args.exchange if world > 1 else 'none'}"},
-            "tflops_dense_eq": dense / (ms / 1e3) / 1e12, "device_status": status,
-        }), flush=True)  # fmt: skip
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    ctx.barrier()
+    ms = ctx.max_over_ranks(timed(step, 2, 5))[0]
+    y = step()
+    err = max(rel_fro(y[i], library_newton_schulz(x[i])) for i in (0, 1, HEAD_CHUNK // 2, HEAD_CHUNK - 1))
+    err = ctx.max_over_ranks(err)[0]
+    dense, _ = flops(*HEAD_SHAPE, NS_STEPS)
+    total = chunks * HEAD_CHUNK * world
+    return {
+        "what": f"{total} matrices of {HEAD_SHAPE[0]}x{HEAD_SHAPE[1]} ({chunks * HEAD_CHUNK} per GPU in chunks of "
+        f"{HEAD_CHUNK}), {NS_STEPS} '{COEFF}' steps each, fp32 in/out",
+        "ms": ms,
+        "matrices_per_s": total / (ms / 1e3),
+        "tflops_dense_eq": total * dense / (ms / 1e3) / 1e12,
+        "rel_fro_vs_library_gemm": err,
+        "device_status": _native.read_device_status(dev),
+    }
+
+
+def run_gpu_arm(args) -> None:
+    ctx = Ctx(args)
+    line = headline_section(ctx, args)
+    if not args.kernels_only and args.sections != "headline":
+        sections = [
+            ("gpu_library_baseline", lambda: library_section(ctx)),
+            ("muon_step", lambda: muon_step_section(ctx, args)),
+            ("per_head", lambda: per_head_section(ctx, args)),
+        ]
+        if ctx.world > 1:
+            sections.insert(2, ("tp_ns", lambda: tp_section(ctx, args)))
+        for name, fn in sections:
+            try:
+                res = fn()
+            except Exception as exc:  # noqa: BLE001  (a failed extra must not cost the headline line)
+                res = {"error": f"{type(exc).__name__}: {exc}"[:400]}
+                if name == "gpu_library_baseline":
+                    res = (res, res)
+            if name == "gpu_library_baseline":
+                line["gpu_library_baseline"], line["syrk_config2"] = res
+            else:
+                line[name] = res
+        if ctx.rank == 0:
+            cpu = cpu_reference(4, 1)
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if ctx.rank == 0:
+        print(json.dumps(line), flush=True)
+    ctx.close()
+
+
+def run_single_section(args) -> None:
+    """One of the secondary workloads on its own (ad-hoc runs): prints that section's object."""
+    ctx = Ctx(args)
+    fn = {"muon_step": muon_step_section, "tp_ns": tp_section, "per_head": per_head_section}[args.workload]
+    res = fn(ctx, args)
+    if ctx.rank == 0:
+        print(json.dumps(dict(res, n_gpus=ctx.world, workload=args.workload)), flush=True)
+    ctx.close()
 
 
 def main() -> None:
@@ -601,12 +875,13 @@ def main() -> None:
                     "--warmup taken as given (for profiler captures; not a benchmark number)")
     ap.add_argument("--exchange", default="ce", choices=["ce", "nccl"],
                     help="N > 1: exchange results by copy-engine pushes into symmetric memory (default) or by NCCL")
-    ap.add_argument("--workload", default="newton_schulz", choices=["newton_schulz", "muon_step", "tp_ns"],
-                    help="newton_schulz (default, the headline metric) or muon_step (BASELINE config 3)")
-    ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step workload")
-    ap.add_argument("--tp-shard-poly-min-world", type=int, default=0,
-                    help="tp_ns: smallest group that computes S = bA + cA^2 in row blocks per rank (0: library default)")
-    ap.add_argument("--lp-exchange", choices=["updates", "parameters"], default="updates",
+    ap.add_argument("--workload", default="all", choices=["all", "muon_step", "tp_ns", "per_head"],
+                    help="all (default): the headline line with every section; or one secondary section alone")
+    ap.add_argument("--sections", default="all", choices=["all", "headline"],
+                    help="headline: only the newton_schulz metric, without the secondary sections")
+    ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step section")
+    ap.add_argument("--muon-steps", type=int, default=5, help="timed steps of the muon_step section")
+    ap.add_argument("--lp-exchange", choices=["updates", "parameters"], default="parameters",
                     help="muon_step: what the layer-parallel optimizer all-gathers")
     ap.add_argument("--bucket-numel", type=int, default=0,
                     help="muon_step: elements per rank and exchange bucket (0: the optimizer's default)")
@@ -616,10 +891,8 @@ def main() -> None:
         M, N_COLS = args.shape
     if args.impl == "reference":
         run_reference_arm(args)
-    elif args.workload == "muon_step":
-        run_muon_step(args)
-    elif args.workload == "tp_ns":
-        run_tp_ns(args)
+    elif args.workload != "all":
+        run_single_section(args)
     else:
         run_gpu_arm(args)
 

@@ -98,9 +98,15 @@ _PROTOTYPES: dict[str, tuple] = {
     "eo_tp_gram_flag_count": (c_size_t, [c_int, c_int]),
     "eo_tp_gram_allreduce": (
         c_int,
-        [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_uint32, c_void_p],
+        [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
+        + [c_int64, c_uint32, c_void_p],
     ),
-    "eo_tp_gram_mirror": (c_int, [c_void_p, c_int, c_int64, c_void_p]),
+    "eo_gemm_multicast": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64]
+        + [c_int, c_int, c_int, c_float, c_float, c_void_p],
+    ),
+    "eo_peek_device_status_async": (c_int, [c_void_p, c_void_p]),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -579,8 +585,14 @@ def newton_schulz_f32(x: torch.Tensor, schedule) -> torch.Tensor:
     return out
 
 
-def tp_gram_allreduce(x: torch.Tensor, world: int, rank: int, inbox_ptrs, flag_ptrs, gram_ptrs, ld_gram: int, seq: int) -> None:
-    """Launch the fused tensor-parallel Gram exchange for this rank's bf16 shard ``x`` (see ``eo_tp_gram_allreduce``)."""
+def tp_gram_allreduce(
+    x: torch.Tensor, world: int, rank: int, partial_ptrs, flag_ptrs, gram_ptrs, partials_mc: int, gram_mc: int,
+    ld_gram: int, seq: int,
+) -> None:  # fmt: skip
+    """Launch the fused tensor-parallel Gram exchange for this rank's bf16 shard ``x`` (see ``eo_tp_gram_allreduce``).
+
+    ``partials_mc`` / ``gram_mc`` are the multicast addresses of the partial-tile buffers and Gram matrices, or 0.
+    """
     require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and x.dim() == 2
     mn, ld, _ = _mat_layout(x)
@@ -591,16 +603,47 @@ def tp_gram_allreduce(x: torch.Tensor, world: int, rank: int, inbox_ptrs, flag_p
             a[i] = p
         return a
 
-    with torch.cuda.device(x.device), _Timed("tp_gram", 2, x.device, timed=True):
+    with torch.cuda.device(x.device), _Timed("tp_gram", 1, x.device, timed=True):
         rc = lib().eo_tp_gram_allreduce(
-            x.data_ptr(), mn, ld, x.size(0), x.size(1), world, rank, arr(inbox_ptrs), arr(flag_ptrs), arr(gram_ptrs),
-            ld_gram, seq, _stream(x),
+            x.data_ptr(), mn, ld, x.size(0), x.size(1), world, rank, arr(partial_ptrs), arr(flag_ptrs), arr(gram_ptrs),
+            partials_mc or None, gram_mc or None, ld_gram, seq, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_tp_gram_allreduce")
 
 
-def tp_gram_mirror(gram: torch.Tensor, n: int, ld: int) -> None:
-    """Copy the lower triangle of the local ``n x n`` Gram buffer onto its upper triangle (after the exchange barrier)."""
-    with torch.cuda.device(gram.device), _Timed("tp_mirror", 1, gram.device):
-        rc = lib().eo_tp_gram_mirror(gram.data_ptr(), n, ld, _stream(gram))
-    _check(rc, "eo_tp_gram_mirror")
+def gemm_multicast(
+    a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None, out_local: torch.Tensor, out_mc_ptr: int,
+    alpha: float = 1.0, beta: float = 0.0,
+) -> None:  # fmt: skip
+    """``alpha * a @ b + beta * c`` stored through the multicast address ``out_mc_ptr`` (see ``eo_gemm_multicast``).
+
+    ``out_local`` is this rank's view of the destination (row-major, same shape as the product); it only supplies
+    the layout, the stores go to ``out_mc_ptr`` and so to the same place in every rank's buffer.
+    """
+    require_cuda(a, "a")
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    M, K = a.shape
+    N = b.size(1)
+    assert b.size(0) == K and tuple(out_local.shape) == (M, N)
+    pa, a_mn, lda, _, _ = _operand(a)
+    pb, bt_mn, ldb, _, _ = _operand(b.mT)
+    ldc = 0
+    if c is not None:
+        c_mn, ldc, _ = _mat_layout(c)
+        assert c_mn == 0 and c.dtype == torch.bfloat16
+    d_mn, ldd, _ = _mat_layout(out_local)
+    assert d_mn == 0 and out_local.dtype == torch.bfloat16
+    with torch.cuda.device(a.device), _Timed("gemm", 1, a.device, timed=True):
+        rc = lib().eo_gemm_multicast(
+            pa, a_mn, lda, pb, bt_mn, ldb, c.data_ptr() if c is not None else None, ldc, out_mc_ptr, ldd,
+            M, N, K, alpha, beta, _stream(a),
+        )  # fmt: skip
+    _check(rc, "eo_gemm_multicast")
+
+
+def peek_device_status_async(pinned: torch.Tensor, device: torch.device) -> None:
+    """Enqueue a copy of the kernels' status word into the pinned int32 tensor ``pinned`` (no synchronisation)."""
+    assert pinned.is_pinned() and pinned.dtype == torch.int32 and pinned.numel() >= 1
+    with torch.cuda.device(device):
+        rc = lib().eo_peek_device_status_async(pinned.data_ptr(), torch.cuda.current_stream(device).cuda_stream)
+    _check(rc, "eo_peek_device_status_async")

@@ -15,7 +15,6 @@
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
 #include "ns_small_sm100.cuh"
-#include "tp_reduce.cuh"
 
 namespace {
 
@@ -53,6 +52,7 @@ __device__ unsigned int g_sched_words[2 * kSchedSlots];
 struct DeviceInfo {
   bool ready = false;
   int sm_count = 0;
+  int clock_khz = 0;  // nominal SM clock, to turn the peer-wait budget into cycles
   unsigned int* status_ptr = nullptr;
   unsigned int* sched_ptr = nullptr;
   unsigned int sched_next = 0;
@@ -63,6 +63,7 @@ DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
+int g_option_peer_wait_ms = 10000;  // eo_set_option("peer_wait_ms"): budget of one wait for other ranks' flags
 
 int device_setup(DeviceInfo** out) {
   int dev = 0;
@@ -80,10 +81,15 @@ int device_setup(DeviceInfo** out) {
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_device_status));
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.noalloc_partials), g_noalloc_partials));
     EO_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.sched_ptr), g_sched_words));
-    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
-    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmSmemBytes));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kGemmTpSmemBytes));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kGemmTpSmemBytes));
+    d.clock_khz = prop.clockRate;
     EO_CUDA(cudaFuncSetAttribute(eo::eo_ns_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kSmallSmemBytes));
     if (g_encode == nullptr) {
@@ -123,15 +129,19 @@ int make_map(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner,
   return EO_OK;
 }
 
-// Tensor-parallel push target of a SYRK launch (see GemmParams::tp_*).
-struct TpPush {
+// Tensor-parallel Gram exchange of a SYRK launch (see GemmParams::tp_*).
+struct TpExchange {
   int world, rank;
   unsigned int seq;
-  void* const* inbox;         // [world] base of every rank's inbox
-  unsigned int* const* flags;  // [world] base of every rank's flag words
+  void* const* partials;       // [world] every rank's partial-tile buffer
+  unsigned int* const* flags;  // [world] every rank's flag words, [world][slots] each
+  void* const* gram;           // [world] every rank's Gram matrix
+  const void* partials_mc;     // multicast alias of the partial-tile buffers, or nullptr
+  void* gram_mc;               // multicast alias of the Gram matrices, or nullptr
+  int64_t ld_gram;
 };
 
-// Tile width of the tensor-parallel Gram exchange; the pushing and the reducing kernel must agree on it.
+// Tile width of the tensor-parallel Gram exchange (buffer sizes and tile numbering depend on it).
 inline int tp_tile_n(int N) { return N > 128 ? 256 : 128; }
 inline int tp_total_tiles(int N) {
   const int bn = tp_tile_n(N), tm = (N + eo::kBlockM - 1) / eo::kBlockM, tn = (N + bn - 1) / bn;
@@ -144,7 +154,8 @@ inline int tp_slots(int N, int world) { return (tp_total_tiles(N) + world - 1) /
 int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t planeA, const void* B, int b_mn,
                 int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
                 int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
-                int round_bf16, int tri, int skip_upper, void* stream, const TpPush* tp = nullptr) {
+                int round_bf16, int tri, int skip_upper, void* stream, const TpExchange* tp = nullptr,
+                int d_multicast = 0) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(EO_ERR_BAD_ARG, "negative size");
@@ -275,12 +286,26 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     p.tp_world = tp->world;
     p.tp_rank = tp->rank;
     p.tp_seq = tp->seq;
-    const int slots = tp_slots(N, tp->world);
-    const int64_t tile_elems = static_cast<int64_t>(eo::kBlockM) * tp_tile_n(N);
+    p.tp_slots = tp_slots(N, tp->world);
+    p.tp_total = tp_total_tiles(N);
+    p.tp_partials = static_cast<unsigned short*>(tp->partials[tp->rank]);
+    p.tp_my_flags = tp->flags[tp->rank];
+    p.tp_partials_mc = static_cast<const unsigned short*>(tp->partials_mc);
+    p.tp_gram_mc = static_cast<unsigned short*>(tp->gram_mc);
+    p.tp_ld = tp->ld_gram;
+    // cycles at the nominal clock; the SMs never run faster than that, so the wait is at least as long as asked
+    p.tp_wait_cycles = static_cast<long long>(g_option_peer_wait_ms) * dev->clock_khz;
     for (int r = 0; r < tp->world; ++r) {
-      p.tp_inbox[r] = static_cast<unsigned short*>(tp->inbox[r]) + static_cast<int64_t>(tp->rank) * slots * tile_elems;
-      p.tp_flags[r] = tp->flags[r] + static_cast<int64_t>(tp->rank) * slots;
+      p.tp_flags[r] = tp->flags[r] + static_cast<int64_t>(tp->rank) * p.tp_slots;
+      p.tp_partials_peer[r] = static_cast<const unsigned short*>(tp->partials[r]);
+      p.tp_gram[r] = static_cast<unsigned short*>(tp->gram[r]);
     }
+  }
+  if (d_multicast) {
+    if (tri || precision != 0 || d_fp32 || N % 32 != 0 || !p.vec_ok)
+      return fail(EO_ERR_BAD_ARG, "multicast output needs a general bf16 product with N a multiple of 32 and "
+                                  "16-byte aligned rows");
+    p.d_mc = 1;
   }
   p.bn = narrow ? 128 : 256;
   p.tiles_n = narrow ? tn128 : tn256;
@@ -295,10 +320,18 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     dev->sched_next++;
   }
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-  if (p.bm == 256)
-    eo::eo_gemm_kernel<2><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
-  else
-    eo::eo_gemm_kernel<1><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (tp != nullptr) {
+    constexpr int threads = eo::kGemmThreads + eo::kTpReducerThreads;
+    if (p.bm == 256)
+      eo::eo_gemm_kernel<2, true><<<grid, threads, eo::kGemmTpSmemBytes, st>>>(maps, p);
+    else
+      eo::eo_gemm_kernel<1, true><<<grid, threads, eo::kGemmTpSmemBytes, st>>>(maps, p);
+  } else if (p.bm == 256) {
+    eo::eo_gemm_kernel<2, false><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, st>>>(maps, p);
+  } else {
+    eo::eo_gemm_kernel<1, false><<<grid, eo::kGemmThreads, eo::kGemmSmemBytes, st>>>(maps, p);
+  }
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }
@@ -316,6 +349,11 @@ int eo_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_tile_m") == 0) {
     if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
     g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "peer_wait_ms") == 0) {
+    if (value < 1 || value > 600000) return fail(EO_ERR_BAD_ARG, "peer_wait_ms must be within 1..600000");
+    g_option_peer_wait_ms = value;
     return EO_OK;
   }
   return fail(EO_ERR_BAD_ARG, "unknown option %s", name);
@@ -347,6 +385,23 @@ int eo_gemm(const void* A, int a_mn_major, int64_t lda, int64_t strideA, int64_t
   return launch_gemm(A, a_mn_major, lda, strideA, planeA, B, b_mn_major, ldb, strideB, planeB, C, ldc, strideC, D, ldd, strideD, batch,
                      M, N, K, alpha, beta, post_scale, precision, d_fp32, round_bf16, /*tri=*/0, /*skip_upper=*/0,
                      stream);
+}
+
+int eo_gemm_multicast(const void* A, int a_mn_major, int64_t lda, const void* B, int b_mn_major, int64_t ldb,
+                      const void* C, int64_t ldc, void* D_multicast, int64_t ldd, int M, int N, int K, float alpha,
+                      float beta, void* stream) {
+  return launch_gemm(A, a_mn_major, lda, 0, 0, B, b_mn_major, ldb, 0, 0, C, ldc, 0, D_multicast, ldd, 0, 1, M, N, K, alpha,
+                     beta, 1.0f, /*precision=*/0, /*d_fp32=*/0, /*round_bf16=*/0, /*tri=*/0, /*skip_upper=*/0, stream,
+                     nullptr, /*d_multicast=*/1);
+}
+
+int eo_peek_device_status_async(uint32_t* pinned_host_code, void* stream) {
+  if (pinned_host_code == nullptr) return fail(EO_ERR_BAD_ARG, "pinned_host_code is NULL");
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  EO_CUDA(cudaMemcpyAsync(pinned_host_code, dev->status_ptr, sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                          static_cast<cudaStream_t>(stream)));
+  return EO_OK;
 }
 
 int eo_syrk(const void* A, int a_trans, int64_t lda, int64_t strideA, int64_t planeA, const void* C, int64_t ldc,
@@ -849,70 +904,33 @@ size_t eo_tp_gram_flag_count(int N, int world) {
 }
 
 int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, int world, int rank,
-                         void* const* inbox_ptrs, void* const* flag_ptrs, void* const* gram_ptrs, int64_t ld_gram,
-                         uint32_t seq, void* stream) {
+                         void* const* partial_ptrs, void* const* flag_ptrs, void* const* gram_ptrs,
+                         const void* partials_multicast, void* gram_multicast, int64_t ld_gram, uint32_t seq,
+                         void* stream) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (world < 2 || world > 8 || rank < 0 || rank >= world) return fail(EO_ERR_BAD_ARG, "world must be 2..8");
   if (N <= 0 || K <= 0 || N % 8 != 0) return fail(EO_ERR_BAD_ARG, "N must be a positive multiple of 8, K positive");
-  if (X == nullptr || inbox_ptrs == nullptr || flag_ptrs == nullptr || gram_ptrs == nullptr)
+  if (X == nullptr || partial_ptrs == nullptr || flag_ptrs == nullptr || gram_ptrs == nullptr)
     return fail(EO_ERR_BAD_ARG, "null pointer");
   if (ld_gram < N || ld_gram % 8 != 0) return fail(EO_ERR_BAD_ARG, "ld_gram must be a multiple of 8 and >= N");
+  if ((partials_multicast == nullptr) != (gram_multicast == nullptr))
+    return fail(EO_ERR_BAD_ARG, "give both multicast aliases or neither");
   for (int r = 0; r < world; ++r) {
-    if (inbox_ptrs[r] == nullptr || flag_ptrs[r] == nullptr || gram_ptrs[r] == nullptr)
+    if (partial_ptrs[r] == nullptr || flag_ptrs[r] == nullptr || gram_ptrs[r] == nullptr)
       return fail(EO_ERR_BAD_ARG, "null peer pointer for rank %d", r);
-    if ((reinterpret_cast<uintptr_t>(inbox_ptrs[r]) | reinterpret_cast<uintptr_t>(gram_ptrs[r])) & 15)
+    if ((reinterpret_cast<uintptr_t>(partial_ptrs[r]) | reinterpret_cast<uintptr_t>(gram_ptrs[r])) & 15)
       return fail(EO_ERR_BAD_ARG, "peer buffers must be 16-byte aligned");
   }
+  if ((reinterpret_cast<uintptr_t>(partials_multicast) | reinterpret_cast<uintptr_t>(gram_multicast)) & 15)
+    return fail(EO_ERR_BAD_ARG, "multicast aliases must be 16-byte aligned");
   unsigned int* flags[8];
   for (int r = 0; r < world; ++r) flags[r] = static_cast<unsigned int*>(flag_ptrs[r]);
-  TpPush tp{world, rank, seq, inbox_ptrs, flags};
-  // 1. partial Gram tiles pushed to their owners from the SYRK epilogue
-  int rc = launch_gemm(X, x_trans, ldx, 0, 0, X, x_trans, ldx, 0, 0, nullptr, 0, 0, nullptr, 0, 0, 1, N, N, K, 1.0f,
-                       0.0f, 1.0f, 0, 0, 0, /*tri=*/1, 0, stream, &tp);
-  if (rc) return rc;
-  // 2. owners reduce their tiles and store them (and their mirror images) into every rank's Gram matrix
-  eo::TpReduceParams q;
-  memset(&q, 0, sizeof(q));
-  q.N = N;
-  q.bn = tp_tile_n(N);
-  q.world = world;
-  q.rank = rank;
-  q.seq = seq;
-  q.tiles_m = (N + eo::kBlockM - 1) / eo::kBlockM;
-  q.tiles_n = (N + q.bn - 1) / q.bn;
-  q.total_tiles = tp_total_tiles(N);
-  q.slots = tp_slots(N, world);
-  q.inbox = static_cast<const unsigned short*>(inbox_ptrs[rank]);
-  q.flags = flags[rank];
-  for (int r = 0; r < world; ++r) q.gram[r] = static_cast<unsigned short*>(gram_ptrs[r]);
-  q.ld = ld_gram;
-  q.status = dev->status_ptr;
-  q.mirror = 0;  // lower triangle only; eo_tp_gram_mirror completes each rank's copy after the barrier
-  const int smem = eo::kBlockM * (q.bn + 8) * 2;
-  static bool attr_set[kMaxDevices] = {};
-  int devid = 0;
-  EO_CUDA(cudaGetDevice(&devid));
-  if (!attr_set[devid]) {
-    EO_CUDA(cudaFuncSetAttribute(eo::tp_gram_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 eo::kBlockM * (256 + 8) * 2));
-    attr_set[devid] = true;
-  }
-  const int grid = q.slots < 2 * dev->sm_count ? q.slots : 2 * dev->sm_count;
-  eo::tp_gram_reduce_kernel<<<grid, eo::kTpReduceThreads, smem, static_cast<cudaStream_t>(stream)>>>(q);
-  EO_CUDA(cudaGetLastError());
-  return EO_OK;
-}
-
-int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream) {
-  DeviceInfo* dev = nullptr;
-  if (int rc = device_setup(&dev)) return rc;
-  if (gram == nullptr || N <= 0 || ld_gram < N) return fail(EO_ERR_BAD_ARG, "bad Gram matrix");
-  const int nb = (N + 31) / 32;
-  eo::mirror_lower_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<unsigned short*>(gram), N, ld_gram);
-  EO_CUDA(cudaGetLastError());
-  return EO_OK;
+  TpExchange tp{world, rank, seq, partial_ptrs, flags, gram_ptrs, partials_multicast, gram_multicast, ld_gram};
+  // One launch: the SYRK main loop, the partial tiles and flags from its epilogue, and the owners' reduction
+  // into every rank's Gram matrix (both triangles) from the reducer warps of the same CTAs.
+  return launch_gemm(X, x_trans, ldx, 0, 0, X, x_trans, ldx, 0, 0, nullptr, 0, 0, nullptr, 0, 0, 1, N, N, K, 1.0f, 0.0f,
+                     1.0f, 0, 0, 0, /*tri=*/1, 0, stream, &tp);
 }
 
 size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }

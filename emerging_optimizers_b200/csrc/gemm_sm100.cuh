@@ -15,6 +15,16 @@
 // TMEM holds two 128 x 256 fp32 accumulators so the epilogue of tile t overlaps the main loop of
 // tile t+1.  Every wait is bounded; a wait that runs out records a code in the status word and the
 // role leaves its loop.
+//
+// Tensor-parallel Gram mode (template parameter kTp, with `tri`): every rank of a tensor-parallel group runs
+// this kernel on its shard and the sum over ranks lands in every rank's Gram matrix before the kernel ends.
+// The epilogue writes each bf16 partial tile into the rank's own symmetric buffer and raises a flag in the
+// memory of the tile's owner rank (tile t belongs to rank t mod P).  Four extra warps per CTA (warps 10..13)
+// are the reducer: for every tile this rank owns they wait (bounded) for the flags of all ranks, read the
+// tile with one NVSwitch load-reduce per 16 bytes (fp32 accumulation in the switch, one rounding) -- or, where
+// no multicast mapping exists, peer by peer with plain loads -- and store the tile and its mirror image into
+// all ranks' Gram matrices with multicast stores (or peer by peer).  Tiles become ready in scheduling order on
+// all ranks at about the same time, so the exchange runs behind the main loop of the following tiles.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -44,6 +54,14 @@ constexpr int kTileQueue = 4;  // depth of the in-CTA queue of tile indices hand
 
 // Shared-memory budget: ring + barriers + tile queue + TMEM address slot, plus slack for 1024-byte alignment.
 constexpr int kGemmSmemBytes = kStages * kStageBytes + 512 + 1024;
+
+// Tensor-parallel Gram mode: the reducer warps and their staging block of 128 rows x 32 columns (bf16, rows padded
+// by 8 elements against bank conflicts when the block is read column-wise for the mirror image).
+constexpr int kTpReducerThreads = 128;
+constexpr int kTpStagePitch = 32 + 8;
+constexpr int kTpStageBytes = kBlockM * kTpStagePitch * 2;
+constexpr int kGemmTpSmemBytes = kGemmSmemBytes + kTpStageBytes;
+constexpr uint32_t kTpPoison = 0x7FC07FC0u;  // two bf16 NaNs: what a reducer that gave up waiting stores
 
 struct GemmParams {
   int batch, M, N, K;
@@ -78,13 +96,23 @@ struct GemmParams {
   // that starts late or shares its SM with another kernel simply takes fewer tiles.  `sched[1]` counts CTAs that
   // have finished; the last one zeroes both words for the next launch that uses this slot.
   unsigned int* sched;
-  // Tensor-parallel Gram mode (tp_world > 1, with tri): instead of storing D, the epilogue pushes the bf16 partial
-  // tile t into the inbox of its owner rank (t % tp_world) - plain stores to local or peer memory - and then
-  // publishes a sequence number in the owner's flag word for (this rank, t / tp_world).
+  // Tensor-parallel Gram mode (tp_world > 1, with tri; see the head of this file).  Tiles are numbered on the
+  // grid of 128-row x bn-column tiles, column block by column block, rows from the diagonal down: tile t is owned
+  // by rank t % tp_world and is that rank's slot t / tp_world.
   int tp_world, tp_rank;
-  unsigned int tp_seq;
-  unsigned short* tp_inbox[8];  // per owner: base of the region this rank writes, [slot][128][bn] bf16
-  unsigned int* tp_flags[8];    // per owner: flag words of this rank, [slot]
+  unsigned int tp_seq;              // sequence number of this exchange (flag value that means "tile written")
+  int tp_slots, tp_total;           // slots per owner; number of tiles
+  unsigned short* tp_partials;      // this rank's partial tiles, [tile][128][bn] bf16 (local memory)
+  unsigned int* tp_flags[8];        // per owner rank: this rank's flag words in the owner's memory, [slot]
+  const unsigned int* tp_my_flags;  // flag words other ranks raise for the tiles this rank owns, [rank][slot]
+  const unsigned short* tp_partials_mc;       // multicast alias of tp_partials (nullptr: read the peers one by one)
+  const unsigned short* tp_partials_peer[8];  // every rank's tp_partials
+  unsigned short* tp_gram_mc;       // multicast alias of the Gram matrices (nullptr: store to the peers one by one)
+  unsigned short* tp_gram[8];       // every rank's Gram matrix, N x tp_ld bf16
+  long long tp_ld;
+  long long tp_wait_cycles;         // budget of one wait for the other ranks' flags
+  // D is a multicast address (general product, bf16 D, N a multiple of 32): every store goes to all ranks.
+  int d_mc;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
@@ -214,7 +242,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
         t.y = static_cast<unsigned int>(h[8 * q + 2]) | (static_cast<unsigned int>(h[8 * q + 3]) << 16);
         t.z = static_cast<unsigned int>(h[8 * q + 4]) | (static_cast<unsigned int>(h[8 * q + 5]) << 16);
         t.w = static_cast<unsigned int>(h[8 * q + 6]) | (static_cast<unsigned int>(h[8 * q + 7]) << 16);
-        reinterpret_cast<uint4*>(drow)[q] = t;
+        if (p.d_mc)
+          multimem_st_16(reinterpret_cast<uint4*>(drow) + q, t);
+        else
+          reinterpret_cast<uint4*>(drow)[q] = t;
       }
     } else {
 #pragma unroll
@@ -237,8 +268,8 @@ struct GemmMaps {
   CUtensorMap b[kMaxPlanes];
 };
 
-// Tensor-parallel push of one 32-column chunk of a partial tile: alpha * acc rounded to bf16, 64 contiguous
-// bytes per thread at [row_local][col_local .. +32) of the tile image in the owner's inbox.
+// Tensor-parallel mode: one 32-column chunk of a partial tile, alpha * acc rounded to bf16, 64 contiguous bytes
+// per thread at [row_local][col_local .. +32) of the tile image in this rank's partial-tile buffer.
 __device__ __forceinline__ void push_chunk(const GemmParams& p, const uint32_t (&acc)[32], unsigned short* tile,
                                            int row_local, int col_local) {
   unsigned short* dst = tile + static_cast<long long>(row_local) * p.bn + col_local;
@@ -258,8 +289,9 @@ __device__ __forceinline__ void push_chunk(const GemmParams& p, const uint32_t (
 
 // kHalves = 1: 128-row tiles, four 48 KiB stages, two alternating accumulators.
 // kHalves = 2: 256-row tiles (two MMAs per k-step on one B tile), three 64 KiB stages, one accumulator per half.
-template <int kHalves>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// kTp: tensor-parallel Gram mode, with four reducer warps after the epilogue warps.
+template <int kHalves, bool kTp>
+__global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 1)
     eo_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle atoms are 1024 bytes: align the ring so that descriptor arithmetic holds.
@@ -273,7 +305,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   uint64_t* tq_empty_bar = tq_full_bar + kTileQueue;  // [kTileQueue]
   int* tile_queue = reinterpret_cast<int*>(tq_empty_bar + kTileQueue);  // [kTileQueue]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_queue + kTileQueue);
-  unsigned int* push_done = tmem_slot + 1;  // [2] epilogue warps that finished pushing the tile in accumulator ab
+  unsigned int* push_done = tmem_slot + 1;  // [2] epilogue warps that finished writing the tile in accumulator ab
+  int* tp_give_up = reinterpret_cast<int*>(push_done + 2);  // reducer: a wait for the other ranks ran out
+  // reducer staging block, behind the 512 bytes of barriers and queues (kTp only)
+  unsigned short* tp_stage = reinterpret_cast<unsigned short*>(smem + kStages * kStageBytes + 512);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -294,6 +329,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     push_done[0] = 0u;
     push_done[1] = 0u;
+    *tp_give_up = 0;
     mbar_init_fence();
     for (int t = 0; t < p.nterms; ++t) {
       tma_prefetch_desc(&maps.a[p.term_a[t]]);
@@ -471,7 +507,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
       }
     }
-  } else {
+  } else if (warp < 2 + kEpilogueWarps) {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
     const int group = (warp - 2) >> 2;     // first or second set of four warps
@@ -511,9 +547,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const long long batch_c = static_cast<long long>(b) * p.strideC;
       const long long batch_d = static_cast<long long>(b) * p.strideD;
       const int nchunks = p.bn / 32;
-      if (p.tp_world > 1) {
-        // Push the partial tile to its owner, then let the last warp working on this accumulator publish the flag.
-        // Owners and inbox slots are defined on the 128-row tile grid; a 256-row tile is two of those.
+      if (kTp) {
+        // Write the partial tile into this rank's buffer, then let the last warp working on this accumulator raise
+        // the flag at the tile's owner.  Owners and slots are defined on the 128-row tile grid; a 256-row tile is
+        // two of those.
         int sub = t;
         bool exists = true;
         if (wide_m) {
@@ -524,7 +561,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         const int owner = sub % p.tp_world;
         const int slot = sub / p.tp_world;
-        unsigned short* tile = p.tp_inbox[owner] + static_cast<long long>(slot) * kBlockM * p.bn;
+        unsigned short* tile = p.tp_partials + static_cast<long long>(sub) * kBlockM * p.bn;
         if (exists) {
           for (int c = chunk0; c < nchunks; c += kChunkStep) {
             uint32_t acc[32];
@@ -544,8 +581,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             push_done[ab] = 0u;
             if (exists) {
               __threadfence_system();
-              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[owner] + slot), "r"(p.tp_seq)
-                           : "memory");
+              st_release_sys_u32(p.tp_flags[owner] + slot, p.tp_seq);
             }
           }
         }
@@ -573,6 +609,137 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         aphase ^= 1u;
       }
     }
+  } else if (kTp) {
+    // ------------------------------------------------------------------ reducer (warps 10..13, kTp only)
+    const int rt = static_cast<int>(threadIdx.x) - kGemmThreads;  // 0..127
+    const int tm128 = (p.M + kBlockM - 1) / kBlockM;
+    const int nsub = p.bn / 32;  // 32-column blocks of a tile
+    bool gave_up = false;
+    for (int slot = blockIdx.x; slot < p.tp_slots; slot += gridDim.x) {
+      const int sub = slot * p.tp_world + p.tp_rank;
+      if (sub >= p.tp_total) break;
+      // tile (ti, tj) on the 128-row grid: column blocks in order, rows from the diagonal down
+      int ti = 0, tj = 0;
+      {
+        int r = sub;
+        for (int j = 0; j < p.tiles_n; ++j) {
+          const int first = (j * p.bn) / kBlockM;
+          const int cnt = tm128 - first;
+          if (r < cnt) {
+            tj = j;
+            ti = first + r;
+            break;
+          }
+          r -= cnt;
+        }
+      }
+      const int m0 = ti * kBlockM, n0 = tj * p.bn;
+      // Wait (bounded) until every rank has written its partial of this tile.
+      if (!gave_up) {
+        if (rt < p.tp_world) {
+          const unsigned int* f = p.tp_my_flags + static_cast<long long>(rt) * p.tp_slots + slot;
+          const long long t0 = clock64();
+          while (static_cast<int>(ld_acquire_sys_u32(f) - p.tp_seq) < 0) {
+            if (clock64() - t0 > p.tp_wait_cycles) {
+              *tp_give_up = 1;
+              report(p, kStatusTimeoutPeer);
+              break;
+            }
+          }
+        }
+        named_barrier_sync(1, kTpReducerThreads);
+        gave_up = (*tp_give_up != 0);
+      }
+      const long long tile_off = static_cast<long long>(sub) * kBlockM * p.bn;
+      for (int cb = 0; cb < nsub; ++cb) {
+        const int col0 = n0 + cb * 32;
+        if (col0 >= p.N || col0 > m0 + kBlockM - 1) break;  // outside the matrix, or wholly above the diagonal
+        // ---- sum over ranks of a 128 x 32 block (512 groups of 8 elements, four per thread), staged in shared
+        //      memory and stored row-wise where it lies on or below the diagonal
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int v = rt + kTpReducerThreads * i;
+          const int r = v >> 2, c8 = (v & 3) * 8;
+          const long long off = tile_off + static_cast<long long>(r) * p.bn + cb * 32 + c8;
+          uint4 w;
+          if (gave_up) {
+            w = make_uint4(kTpPoison, kTpPoison, kTpPoison, kTpPoison);
+          } else if (p.tp_partials_mc != nullptr) {
+            w = multimem_ld_reduce_bf16x8(p.tp_partials_mc + off);
+          } else {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int src = 0; src < p.tp_world; ++src) {
+              const uint4 x = ld_relaxed_sys_16(p.tp_partials_peer[src] + off);
+              const unsigned int xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc[2 * e] += __uint_as_float(xs[e] << 16);
+                acc[2 * e + 1] += __uint_as_float(xs[e] & 0xFFFF0000u);
+              }
+            }
+            unsigned int o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              o[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * e]))) |
+                     (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * e + 1]))) << 16);
+            w = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          *reinterpret_cast<uint4*>(tp_stage + r * kTpStagePitch + c8) = w;
+          const int row = m0 + r, col = col0 + c8;
+          if (row < p.N && col <= row) {
+            const long long at = static_cast<long long>(row) * p.tp_ld + col;
+            if (col + 7 <= row) {  // col + 7 <= row < N: the whole group lies inside the lower triangle
+              if (p.tp_gram_mc != nullptr) {
+                multimem_st_16(p.tp_gram_mc + at, w);
+              } else {
+                for (int d = 0; d < p.tp_world; ++d) *reinterpret_cast<uint4*>(p.tp_gram[d] + at) = w;
+              }
+            } else {
+              const unsigned int ws[4] = {w.x, w.y, w.z, w.w};
+              for (int e = 0; e < 8; ++e) {
+                if (col + e > row) break;
+                const unsigned short h = static_cast<unsigned short>(ws[e >> 1] >> ((e & 1) * 16));
+                for (int d = 0; d < p.tp_world; ++d) p.tp_gram[d][at + e] = h;
+              }
+            }
+          }
+        }
+        named_barrier_sync(1, kTpReducerThreads);
+        // ---- mirror image: element (row, col), col < row, also goes to (col, row); eight rows per group so that
+        //      the stores run along the rows of the destination
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int v = rt + kTpReducerThreads * i;
+          const int c = v >> 4, r8 = (v & 15) * 8;
+          const int col = col0 + c, row = m0 + r8;
+          if (col < p.N && row < p.N && col < row + 7) {  // some element of the group lies below the diagonal
+            const long long at = static_cast<long long>(col) * p.tp_ld + row;
+            const unsigned short* sp = tp_stage + r8 * kTpStagePitch + c;
+            if (col < row && row + 7 < p.N) {
+              uint4 w;
+              w.x = sp[0] | (static_cast<unsigned int>(sp[kTpStagePitch]) << 16);
+              w.y = sp[2 * kTpStagePitch] | (static_cast<unsigned int>(sp[3 * kTpStagePitch]) << 16);
+              w.z = sp[4 * kTpStagePitch] | (static_cast<unsigned int>(sp[5 * kTpStagePitch]) << 16);
+              w.w = sp[6 * kTpStagePitch] | (static_cast<unsigned int>(sp[7 * kTpStagePitch]) << 16);
+              if (p.tp_gram_mc != nullptr) {
+                multimem_st_16(p.tp_gram_mc + at, w);
+              } else {
+                for (int d = 0; d < p.tp_world; ++d) *reinterpret_cast<uint4*>(p.tp_gram[d] + at) = w;
+              }
+            } else {
+              for (int e = 0; e < 8; ++e) {
+                if (col < row + e && row + e < p.N)
+                  for (int d = 0; d < p.tp_world; ++d) p.tp_gram[d][at + e] = sp[e * kTpStagePitch];
+              }
+            }
+          }
+        }
+        named_barrier_sync(1, kTpReducerThreads);
+      }
+    }
+    // every store of this rank's reducers is visible system-wide before the kernel (and the group barrier the host
+    // enqueues behind it) completes
+    __threadfence_system();
   }
 
   tc_fence_before();

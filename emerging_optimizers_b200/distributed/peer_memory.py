@@ -7,13 +7,17 @@ peer's buffer with an ordinary device-to-device copy or an ordinary store from a
 - :meth:`PeerBuffer.all_gather_slots`: an all-gather made of copy-engine transfers (one ``cudaMemcpyAsync`` per
   peer, on its own stream) followed by a group barrier.  It occupies no SM, so it does not take SMs away from the
   persistent tensor-core kernels it overlaps with, which a kernel-based collective does.
-- the raw peer pointers (:attr:`PeerBuffer.ptrs`) handed to kernels that store to peers directly.
+- the raw peer pointers (:attr:`PeerBuffer.ptrs`) and the NVSwitch multicast address
+  (:attr:`PeerBuffer.multicast_ptr`, 0 if the box has no multicast support or ``EO_MULTICAST=0``) handed to kernels
+  that load from / store to peers directly.
 
-Only plain copies, plain loads/stores and the library's own barrier touch peer memory; no TMA load with cluster
-multicast ever reads it.
+Only plain copies, plain loads/stores, ``multimem`` load-reduce / stores and the library's own barrier touch peer
+memory; no TMA load with cluster multicast ever reads it.
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 import torch.distributed as dist
@@ -37,7 +41,14 @@ class PeerBuffer:
         self.numel, self.dtype, self.device = numel, dtype, device
         self.local = symm.empty(numel, dtype=dtype, device=device)
         self.handle = symm.rendezvous(self.local, self.group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # Addresses of element 0 on every rank, and through the multicast (NVLS) mapping if the box has one.  The
+        # handle describes the allocation the tensor lives in; the tensor's offset inside it is the same on all
+        # ranks and is taken from this rank's own pair of addresses.
+        base = [int(p) for p in self.handle.buffer_ptrs]
+        delta = self.local.data_ptr() - base[self.rank]
+        self.ptrs = [p + delta for p in base]
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.multicast_ptr = mc + delta if mc and os.environ.get("EO_MULTICAST", "1") != "0" else 0
         self._copy_streams = [torch.cuda.Stream(device=device) for _ in range(max(self.world - 1, 1))]
 
     def peer_view(self, peer: int, numel: int, offset: int = 0) -> torch.Tensor:

@@ -13,6 +13,8 @@ product of the last step writes fp32 directly.  There is no CPU path: CPU tensor
 
 from __future__ import annotations
 
+import os
+
 from itertools import chain, cycle, islice, repeat
 from typing import Any, Iterator, Literal, Sequence
 
@@ -240,6 +242,13 @@ def _gram_poly_sharded(
         return None
     if m % (8 * world) != 0 or not A.is_contiguous():
         return None
+    from emerging_optimizers_b200.distributed import tensor_parallel
+
+    if os.environ.get("EO_TP_GRAM", "auto") != "nccl":
+        # product + all-gather in one kernel: the epilogue stores this rank's rows into every rank's buffer
+        S = tensor_parallel.sharded_gram_poly(A, b, c, tp_group)
+        if S is not None:
+            return S
     rows = m // world
     r0 = torch.distributed.get_rank(tp_group) * rows
     S = torch.empty((m, m), dtype=A.dtype, device=A.device)

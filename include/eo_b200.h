@@ -43,7 +43,9 @@ const char* eo_last_error(void);
 /*
  * Tuning knobs (process-wide).  "gemm_tile_m": 0 (default) lets each launch choose between 128-row tiles and
  * 256-row tiles (two MMAs per k-step sharing one B tile: fewer operand bytes per FLOP, used for large problems
- * with long K); 128 or 256 forces one.  Results do not depend on the choice.
+ * with long K); 128 or 256 forces one.  Results do not depend on the choice.  "peer_wait_ms" (default 10000):
+ * how long a kernel waits for a flag that another rank has to raise before it gives up (see
+ * eo_tp_gram_allreduce).
  */
 int eo_set_option(const char* name, int value);
 
@@ -272,26 +274,27 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
                          size_t workspace_bytes, void* stream);
 
 /*
- * Tensor-parallel Gram matrix with the all-reduce fused into the SYRK epilogue (one NVSwitch box, 2..8 ranks).
+ * Tensor-parallel Gram matrix: SYRK and all-reduce in ONE kernel (one NVSwitch box, 2..8 ranks).
  *
  * Every rank holds a shard X_r (N x K_r, bf16; `x_trans` as `a_trans` of eo_syrk) of a matrix sharded along
- * the contraction dimension.  The call computes the partial Gram X_r X_r^T tile by tile; the epilogue of tile t
- * stores the bf16 partial straight into the inbox of the tile's owner (rank t mod world) - a plain store to
- * local or peer memory - and publishes `seq` in the owner's flag word.  A second kernel on the owner waits
- * (bounded, about one second; on expiry the device status word is set and the kernel returns) for all
- * `world` partials of each of its tiles, sums them in fp32, rounds to bf16 once and stores the lower-triangle part
- * of the tile into the Gram matrix of every rank.  Only lower-triangle data travels: about half the bytes of an
- * all-reduce of the full matrix, and the pushes overlap the main loop of the following tiles.  After the barrier
- * that closes the exchange every rank completes its own copy with eo_tp_gram_mirror (lower -> upper triangle).
+ * the contraction dimension, and all ranks make this call.  The kernel computes the partial Gram X_r X_r^T tile by
+ * tile (lower-triangle tiles only).  The epilogue of tile t writes the bf16 partial into the rank's own partial
+ * buffer and publishes `seq` in a flag word of the tile's owner (rank t mod world).  Reducer warps of the same
+ * CTAs serve the tiles this rank owns: they wait for the `world` flags of a tile (bounded by the option
+ * "peer_wait_ms", default 10 s; on expiry the device status word is set and the tile is filled with NaN on every
+ * rank, so that a failed exchange cannot pass for a result), sum the partials in fp32 with one rounding - one
+ * NVSwitch load-reduce per 16 bytes when the multicast aliases are given, plain loads from every peer otherwise -
+ * and store the tile and its mirror image into the Gram matrix of every rank (multicast stores, or one store per
+ * peer).  The exchange of a tile overlaps the main loop of the following tiles.
  *
- * inbox_ptrs / flag_ptrs / gram_ptrs: host arrays of `world` device pointers, entry r addressing rank r's
- * buffer (peer-mapped, e.g. symmetric memory): inbox of eo_tp_gram_inbox_bytes(N, world) bytes, flags of
+ * partial_ptrs / flag_ptrs / gram_ptrs: host arrays of `world` device pointers, entry r addressing rank r's
+ * buffer (peer-mapped, e.g. symmetric memory): partial tiles of eo_tp_gram_inbox_bytes(N, world) bytes, flags of
  * eo_tp_gram_flag_count(N, world) uint32 (zeroed once at creation), Gram matrix N x ld_gram bf16.
- * `seq` must increase by one with every call on the same buffers (first call: 1).  After the call, a
- * barrier across the ranks that orders the owners' stores, and eo_tp_gram_mirror on the local matrix, every
- * rank's Gram matrix holds the full symmetric sum.
- * The caller must also order the next call after all ranks have consumed their Gram matrix (the same barrier
- * does both when each rank uses the matrix before its next call).
+ * partials_multicast / gram_multicast: multicast (NVLS) addresses mapping all ranks' partial buffers / Gram
+ * matrices, or both NULL.  `seq` must increase by one with every call on the same buffers (first call: 1).
+ * After the call and a barrier across the ranks (which orders the owners' stores before the readers, and every
+ * rank's reads of the partial buffers before the next call overwrites them) every rank's Gram matrix holds the
+ * full symmetric sum.
  *
  * Stands in for tsyrk_ex + torch.distributed.all_reduce at
  * emerging_optimizers/orthogonalized_optimizers/muon_utils.py:434-436 (and :370-372).
@@ -299,9 +302,30 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
 size_t eo_tp_gram_inbox_bytes(int N, int world);
 size_t eo_tp_gram_flag_count(int N, int world);
 int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, int world, int rank,
-                         void* const* inbox_ptrs, void* const* flag_ptrs, void* const* gram_ptrs, int64_t ld_gram,
-                         uint32_t seq, void* stream);
-int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream);
+                         void* const* partial_ptrs, void* const* flag_ptrs, void* const* gram_ptrs,
+                         const void* partials_multicast, void* gram_multicast, int64_t ld_gram, uint32_t seq,
+                         void* stream);
+
+/*
+ * General bf16 product D = alpha * op(A) op(B)^T + beta * C (single matrix, conventions of eo_gemm) whose result
+ * is stored through a multicast (NVLS) address: every element lands in the buffer of every rank mapped by
+ * `D_multicast`.  With each rank computing a block of rows of one matrix this is "product + all-gather" in one
+ * kernel; the tensor-parallel iteration uses it for S = b A + c A^2 (a rank's row block costs 2 N^3 / world FLOP
+ * instead of N^3 for the redundant symmetric product).  N must be a multiple of 32, rows 16-byte aligned; C is
+ * read from local memory.  The caller orders readers behind a barrier across the ranks.
+ *
+ * Stands in for torch.addmm at emerging_optimizers/orthogonalized_optimizers/muon_utils.py:374 under
+ * tensor parallelism (:277-345), where the reference computes S redundantly on every rank.
+ */
+int eo_gemm_multicast(const void* A, int a_mn_major, int64_t lda, const void* B, int b_mn_major, int64_t ldb,
+                      const void* C, int64_t ldc, void* D_multicast, int64_t ldd, int M, int N, int K, float alpha,
+                      float beta, void* stream);
+
+/*
+ * Enqueues a copy of the device status word (see eo_read_device_status) into `pinned_host_code` on `stream`
+ * without synchronising and without clearing it: a caller polls the host word later, e.g. at its next call.
+ */
+int eo_peek_device_status_async(uint32_t* pinned_host_code, void* stream);
 
 #ifdef __cplusplus
 }

@@ -32,8 +32,9 @@ def _rel(a, b):
     return float((a.double() - b.double()).norm() / b.double().norm())
 
 
-def _worker(rank, world, port, out):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+def _worker(rank, world, port, out, multicast="1"):
+    # EO_MULTICAST=0 keeps the exchange on plain peer loads / stores (what a box without NVLS support runs)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", EO_MULTICAST=multicast)
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -82,6 +83,7 @@ def _worker(rank, world, port, out):
         finally:
             muon_utils.TP_SHARD_GRAM_POLY_MIN_WORLD = saved
     res["sharded_poly"] = bool(torch.equal(y_plain, y_sharded))
+    res["multicast"] = bool(tp._exchange(512, group, dev).multicast)
     torch.cuda.synchronize()
     res["status"] = nat.read_device_status(dev)
     out[rank] = res
@@ -89,15 +91,18 @@ def _worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_fused_gram_exchange_and_tp_newton_schulz_two_gpus():
+@pytest.mark.parametrize("multicast", ["1", "0"])
+def test_fused_gram_exchange_and_tp_newton_schulz_two_gpus(multicast):
     world = 2
     with mp.Manager() as mgr:
         out = mgr.dict()
-        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), out, multicast), nprocs=world, join=True)
         results = dict(out)
     for rank in range(world):
         res = results[rank]
         assert res["status"] == 0
+        if multicast == "0":
+            assert not res["multicast"]
         for key, val in res.items():
             if key.startswith("gram."):
                 assert val, (rank, key)

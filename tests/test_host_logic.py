@@ -269,13 +269,14 @@ def test_fused_step_batch_plan_groups_equal_shapes_within_a_byte_budget():
     assert not _fused_step.eligible(p, None)
 
 
-def test_tp_exchange_is_chosen_by_group_size(monkeypatch):
+def test_tp_exchange_needs_a_group_and_cuda_shards(monkeypatch):
     from emerging_optimizers_b200.distributed import tensor_parallel as tp
 
     x = torch.zeros(8, 8, dtype=torch.bfloat16)
     assert not tp.fused_gram_available(x, None)
     assert not tp.fused_gram_available(x, object())  # CPU tensor: never
-    assert tp.FUSED_MAX_WORLD == 2
+    assert tp.sharded_gram_poly(x, 1.0, 1.0, object()) is None  # likewise
+    tp.clear()  # dropping the (empty) cache is harmless
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

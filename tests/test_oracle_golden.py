@@ -125,3 +125,24 @@ def test_integer_syrk_is_exact():
     d = orc.syrk_ex(a, c, alpha=0.5, beta=0.25)
     assert np.array_equal(d, orc.bf16_round(0.5 * (a @ a.T) + 0.25 * c))
     assert np.array_equal(d, d.T)
+
+
+@pytest.mark.parametrize("precision,tol", [("highest", 2e-5), ("medium", 1.2e-2)])
+def test_torch_cpu_restatement_matches_reference(golden_dir, precision, tol):
+    """The torch-operator restatement timed as the CPU baseline (oracle/ns_torch_cpu.py) against the reference's
+    vectors; only the cases its reduced signature covers (preset schedules, default orientation and eps)."""
+    torch = pytest.importorskip("torch")
+    from oracle import ns_torch_cpu
+
+    data = np.load(os.path.join(golden_dir, f"ns_{precision}.npz"))
+    checked = 0
+    for name, meta in _cases(golden_dir).items():
+        kw = dict(meta["kwargs"])
+        if set(kw) - {"steps", "coefficient_type"} or kw["coefficient_type"] == "custom":
+            continue
+        y = ns_torch_cpu.newton_schulz(torch.from_numpy(data[f"{name}.x"]), kw["steps"], kw["coefficient_type"], precision)
+        ref = data[f"{name}.y"]
+        assert tuple(y.shape) == ref.shape and y.dtype == torch.float32
+        assert rel_fro(y.contiguous().numpy(), ref) <= tol, (name, rel_fro(y.contiguous().numpy(), ref))
+        checked += 1
+    assert checked >= 12
