@@ -4,17 +4,22 @@
 // S = b A + c A^2 never have to leave the SM.  A CTA takes one matrix at a time (dynamic counter) and runs all
 // iterations on it:
 //
-//   Gram   : X streamed through a shared-memory ring in 128 x 64 boxes (K-major), accumulated in TMEM;
-//            the epilogue rounds A to bf16 and writes it into shared memory in the 128B-swizzled operand layout
+//   Gram   : first iteration only as a pass of its own: X streamed through a shared-memory ring in 128 x 64
+//            boxes (K-major), accumulated in TMEM; the epilogue rounds A to bf16 and writes it into shared
+//            memory in the 128B-swizzled operand layout
 //   A^2    : tcgen05.mma on the shared-memory copy of A (skipped when c == 0); epilogue writes S likewise
 //   S X    : X streamed again, 128 x 128 output tiles (the same boxes now act as MN-major B operands, two
-//            N = 64 MMAs per k-step); the epilogue takes the a X term from the boxes still sitting in the ring,
-//            overwrites them in place with the new iterate and a store warp sends them out with TMA stores
-//            (no scattered global loads or stores)
+//            N = 64 MMAs per k-step); the epilogue takes the a X term from the boxes still sitting in the ring
+//            and overwrites them in place with the new iterate.  While a finished tile is still in the ring
+//            it is used twice: a store warp sends it out with TMA stores, and the MMA warp accumulates its
+//            contribution to the NEXT iteration's Gram matrix (the boxes are K-major operands of X' X'^T).
 //
-// so per iteration a matrix is read twice and written once, with no launch boundary, no global A / S traffic and
-// no per-launch tail.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue, warp 10 TMA stores.
-// Every wait is bounded; a wait that runs out records a code in the status word and the CTA drains.
+// so the first iteration reads a matrix twice and every iteration reads it once and writes it once, with no
+// launch boundary, no global A / S traffic and no per-launch tail: 11 passes over the matrix for five steps
+// instead of 15.  The products are accumulated in the same order as by separate passes, so results are
+// bit-identical to the general kernels.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue,
+// warp 10 TMA stores.  Every wait is bounded; a wait that runs out records a code in the status word and the
+// CTA drains.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -29,7 +34,9 @@ constexpr int kSmallABytes = 2 * kSmallUnitBytes;  // 128 x 128 bf16 operand (tw
 constexpr int kSmallThreads = 64 + 32 * 8 + 32;
 constexpr int kSmallSmemBytes = kSmallUnits * kSmallUnitBytes + 2 * kSmallABytes + 1024 + 1024;
 constexpr int kSmallMaxSteps = 16;
-constexpr int kSmallAcc = 4;       // TMEM accumulators of 128 columns each, used round-robin by every product
+constexpr int kSmallAcc = 3;       // TMEM accumulators of 128 columns each, used round-robin by the S X tiles
+constexpr int kSmallAccG = 3;      // index of the fourth accumulator: Gram matrix, then A^2, of one iteration
+constexpr int kSmallGramLag = 2;   // the Gram MMAs of an S X tile are issued this many tiles behind its S X MMAs
 constexpr int kSmallTileN = 128;   // output tile width of the S X product
 constexpr uint32_t kStatusSmall = 0x50u;
 
@@ -64,16 +71,16 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
   uint8_t* a_buf = smem + kSmallUnits * kSmallUnitBytes;
   uint8_t* s_buf = a_buf + kSmallABytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_buf + kSmallABytes);
-  uint64_t* full_bar = bars;                       // [kSmallUnits]
-  uint64_t* empty_bar = full_bar + kSmallUnits;    // [kSmallUnits]
-  uint64_t* acc_full_bar = empty_bar + kSmallUnits;  // [kSmallAcc]
-  uint64_t* acc_empty_bar = acc_full_bar + kSmallAcc;  // [kSmallAcc]
-  uint64_t* a_ready_bar = acc_empty_bar + kSmallAcc;   // A written to shared memory
-  uint64_t* s_ready_bar = a_ready_bar + 1;           // S written to shared memory
-  uint64_t* x_ready_bar = s_ready_bar + 1;           // every tile of the next iterate written to global memory
-  uint64_t* st_ready_bar = x_ready_bar + 1;          // [kSmallAcc] output tile complete in the ring units
-  uint64_t* mq_full_bar = st_ready_bar + kSmallAcc;  // [2] matrix-index queue
-  uint64_t* mq_empty_bar = mq_full_bar + 2;          // [2]
+  uint64_t* full_bar = bars;                           // [kSmallUnits] box loaded
+  uint64_t* empty_bar = full_bar + kSmallUnits;        // [kSmallUnits] box free again (two arrivals, see below)
+  uint64_t* st_ready_bar = empty_bar + kSmallUnits;    // [kSmallUnits] by first box of a tile: new iterate written
+  uint64_t* acc_full_bar = st_ready_bar + kSmallUnits;     // [kSmallAcc + 1]
+  uint64_t* acc_empty_bar = acc_full_bar + kSmallAcc + 1;  // [kSmallAcc + 1]
+  uint64_t* a_ready_bar = acc_empty_bar + kSmallAcc + 1;   // A written to shared memory
+  uint64_t* s_ready_bar = a_ready_bar + 1;             // S written to shared memory
+  uint64_t* x_ready_bar = s_ready_bar + 1;             // every tile of the next iterate written to global memory
+  uint64_t* mq_full_bar = x_ready_bar + 1;             // [2] matrix-index queue
+  uint64_t* mq_empty_bar = mq_full_bar + 2;            // [2]
   int* mat_queue = reinterpret_cast<int*>(mq_empty_bar + 2);  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mat_queue + 2);
 
@@ -82,15 +89,19 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
   const int nk = (p.n + 63) / 64;      // Gram k-blocks
   const int nt = (p.n + kSmallTileN - 1) / kSmallTileN;  // output tiles of the S X product
 
+  // A box is handed back to the producer by two arrivals on its `empty` barrier.  Gram pass of the first
+  // iteration: both from the MMA thread (one at once, one when its MMAs have read the box).  S X pass: one from
+  // the store thread (TMA store has read the box) and one from the MMA thread (the Gram MMAs of the next iteration
+  // have read it); in the last iteration, where neither happens, the store thread arrives twice.
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSmallUnits; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&empty_bar[s], 2);
+      mbar_init(&st_ready_bar[s], 8);
     }
-    for (int s = 0; s < kSmallAcc; ++s) {
+    for (int s = 0; s < kSmallAcc + 1; ++s) {
       mbar_init(&acc_full_bar[s], 1);
       mbar_init(&acc_empty_bar[s], 8);
-      mbar_init(&st_ready_bar[s], 8);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&mq_full_bar[s], 1);
@@ -115,6 +126,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
   auto fail = [&](uint32_t code) {
     if (p.status != nullptr) atomicCAS(p.status, 0u, kStatusSmall + code);
   };
+  auto next_unit = [](int u) { return (u + 1 == kSmallUnits) ? 0 : u + 1; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -161,12 +173,13 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
               break;
             }
             x_phase ^= 1u;
+          } else {
+            for (int kb = 0; kb < nk && ok; ++kb) ok = load_unit(map, kb * 64, b);  // Gram pass of the input
           }
-          for (int kb = 0; kb < nk && ok; ++kb) ok = load_unit(map, kb * 64, b);
           for (int t = 0; t < nt && ok; ++t)
             for (int q = 0; q < 2 && ok; ++q) ok = load_unit(map, t * kSmallTileN + q * 64, b);
         }
-        // The epilogue warps also arrive on x_ready after the last iteration: consume that phase.
+        // The store thread also arrives on x_ready after the last iteration: consume that phase.
         if (ok && p.steps > 0) {
           if (!mbar_wait(x_ready_bar, x_phase)) {
             fail(3);
@@ -182,19 +195,15 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
       const uint32_t idesc_gram = make_idesc(1u, false, false, 128, 128);  // K-major x K-major
       const uint32_t idesc_sx = make_idesc(1u, false, true, 128, 64);      // S K-major, X box MN-major
       const uint32_t a_addr = smem_u32(a_buf), s_addr = smem_u32(s_buf);
+      const uint32_t acc_g = tmem_base + static_cast<uint32_t>(kSmallAccG * 128);
       int unit = 0;
       uint32_t uphase = 0;
       int ab = 0;
-      uint32_t aphase = 0, a_phase = 0, s_phase = 0;
+      uint32_t aphase = 0, g_phase = 0, a_phase = 0, s_phase = 0;
+      uint32_t st_bits = 0;  // phase parity of every st_ready barrier, as seen by this thread
       int mq = 0;
       uint32_t mq_phase = 0;
       bool ok = true;
-      auto next_acc = [&]() {
-        if (++ab == kSmallAcc) {
-          ab = 0;
-          aphase ^= 1u;
-        }
-      };
       auto wait_unit = [&]() -> bool {
         if (!mbar_wait(&full_bar[unit], uphase)) {
           fail(4);
@@ -203,11 +212,31 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         tc_fence_after();
         return true;
       };
-      auto release_unit = [&]() {
-        umma_commit(&empty_bar[unit]);
+      auto advance_unit = [&]() {
         if (++unit == kSmallUnits) {
           unit = 0;
           uphase ^= 1u;
+        }
+      };
+      auto wait_acc_g = [&]() -> bool {  // the epilogue has drained the previous contents of the Gram accumulator
+        if (!mbar_wait(&acc_empty_bar[kSmallAccG], g_phase ^ 1u)) {
+          fail(6);
+          return false;
+        }
+        tc_fence_after();
+        return true;
+      };
+      auto commit_acc_g = [&]() {
+        umma_commit(&acc_full_bar[kSmallAccG]);
+        g_phase ^= 1u;
+      };
+      // X X^T contribution of one 128 x 64 box (K-major operand on both sides)
+      auto gram_box = [&](int u, bool first) {
+        const uint32_t addr = smem_u32(ring + u * kSmallUnitBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t d = make_smem_desc(addr + k * 32u, 0u, 1024u);
+          umma_f16(acc_g, d, d, idesc_gram, (first && k == 0) ? 0u : 1u);
         }
       };
       while (ok) {
@@ -222,75 +251,78 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           mq_phase ^= 1u;
         }
         if (b < 0) break;
-        for (int it = 0; it < p.steps && ok; ++it) {
-          const bool quintic = p.abc[3 * it + 2] != 0.0f;
-          // ---- Gram
-          if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
-            fail(6);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          uint32_t acc = tmem_base + static_cast<uint32_t>(ab * 128);
+        // ---- Gram matrix of the input: a pass of its own
+        if (p.steps > 0) {
+          ok = wait_acc_g();
           for (int kb = 0; kb < nk && ok; ++kb) {
             ok = wait_unit();
             if (!ok) break;
-            const uint32_t u = smem_u32(ring + unit * kSmallUnitBytes);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t d = make_smem_desc(u + k * 32u, 0u, 1024u);
-              umma_f16(acc, d, d, idesc_gram, (kb | k) != 0 ? 1u : 0u);
-            }
-            release_unit();
+            gram_box(unit, kb == 0);
+            mbar_arrive(&empty_bar[unit]);
+            umma_commit(&empty_bar[unit]);
+            advance_unit();
           }
-          if (!ok) break;
-          umma_commit(&acc_full_bar[ab]);
-          next_acc();
-          // ---- A^2 (quintic steps only)
+          if (ok) commit_acc_g();
+        }
+        for (int it = 0; it < p.steps && ok; ++it) {
+          const bool quintic = p.abc[3 * it + 2] != 0.0f;
+          const bool last = (it == p.steps - 1);
+          // ---- A^2 (quintic steps only), into the accumulator the Gram epilogue has just drained
           if (quintic) {
-            {
-              if (!mbar_wait(a_ready_bar, a_phase)) {
-                fail(7);
-                ok = false;
-                break;
-              }
+            if (!mbar_wait(a_ready_bar, a_phase)) {
+              fail(7);
+              ok = false;
+              break;
             }
+            ok = wait_acc_g();
+            if (!ok) break;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint64_t d = make_smem_desc(a_addr + (k >> 2) * kSmallUnitBytes + (k & 3) * 32u, 0u, 1024u);
+              umma_f16(acc_g, d, d, idesc_gram, k != 0 ? 1u : 0u);
+            }
+            commit_acc_g();
+          }
+          a_phase ^= 1u;
+          // ---- S X (S is A itself on cubic steps), with the next iteration's Gram matrix riding behind it
+          if (!mbar_wait(s_ready_bar, s_phase)) {
+            fail(8);
+            ok = false;
+            break;
+          }
+          s_phase ^= 1u;
+          if (!last) {
+            ok = wait_acc_g();
+            if (!ok) break;
+          }
+          const uint32_t s_op = quintic ? s_addr : a_addr;
+          int gunit = unit;   // first box of the oldest tile whose Gram contribution has not been issued yet
+          int pending = 0;    // tiles between the S X front and the Gram front
+          bool gram_first = true;
+          auto gram_tile = [&]() -> bool {
+            const int u0 = gunit, u1 = next_unit(u0);
+            if (!mbar_wait(&st_ready_bar[u0], (st_bits >> u0) & 1u)) {
+              fail(13);
+              return false;
+            }
+            st_bits ^= (1u << u0);
+            tc_fence_after();
+            gram_box(u0, gram_first);
+            gram_box(u1, false);
+            gram_first = false;
+            umma_commit(&empty_bar[u0]);
+            umma_commit(&empty_bar[u1]);
+            gunit = next_unit(u1);
+            return true;
+          };
+          for (int t = 0; t < nt && ok; ++t) {
             if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
               fail(6);
               ok = false;
               break;
             }
             tc_fence_after();
-            acc = tmem_base + static_cast<uint32_t>(ab * 128);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint64_t d = make_smem_desc(a_addr + (k >> 2) * kSmallUnitBytes + (k & 3) * 32u, 0u, 1024u);
-              umma_f16(acc, d, d, idesc_gram, k != 0 ? 1u : 0u);
-            }
-            umma_commit(&acc_full_bar[ab]);
-            next_acc();
-          }
-          a_phase ^= 1u;
-          // ---- S X (S is A itself on cubic steps)
-          {
-            if (!mbar_wait(s_ready_bar, s_phase)) {
-              fail(8);
-              ok = false;
-              break;
-            }
-          }
-          s_phase ^= 1u;
-          const uint32_t s_op = quintic ? s_addr : a_addr;
-          for (int t = 0; t < nt && ok; ++t) {
-            {
-              if (!mbar_wait(&acc_empty_bar[ab], aphase ^ 1u)) {
-                fail(6);
-                ok = false;
-                break;
-              }
-            }
-            tc_fence_after();
-            acc = tmem_base + static_cast<uint32_t>(ab * 128);
+            const uint32_t acc = tmem_base + static_cast<uint32_t>(ab * 128);
             for (int q = 0; q < 2 && ok; ++q) {
               ok = wait_unit();
               if (!ok) break;
@@ -301,15 +333,35 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
                 const uint64_t db = make_smem_desc(u + k * 2048u, 0u, 1024u);
                 umma_f16(acc + static_cast<uint32_t>(q * 64), da, db, idesc_sx, k != 0 ? 1u : 0u);
               }
-              // not released here: the epilogue reuses the unit, the store warp frees it
-              if (++unit == kSmallUnits) {
-                unit = 0;
-                uphase ^= 1u;
-              }
+              advance_unit();  // not released here: the epilogue rewrites the box, store thread and Gram MMAs free it
             }
             if (!ok) break;
             umma_commit(&acc_full_bar[ab]);
-            next_acc();
+            if (++ab == kSmallAcc) {
+              ab = 0;
+              aphase ^= 1u;
+            }
+            if (!last) {
+              ++pending;
+              if (pending > kSmallGramLag) {
+                ok = gram_tile();
+                --pending;
+              }
+            }
+          }
+          if (!last) {
+            while (ok && pending > 0) {
+              ok = gram_tile();
+              --pending;
+            }
+            if (ok) commit_acc_g();
+          } else {
+            // the store thread consumed this iteration's st_ready phases on its own: keep the parities in step
+            int u0 = gunit;
+            for (int t = 0; t < nt; ++t) {
+              st_bits ^= (1u << u0);
+              u0 = next_unit(next_unit(u0));
+            }
           }
         }
       }
@@ -320,25 +372,30 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
     const int chunk0 = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     int ab = 0;
-    uint32_t aphase = 0;
+    uint32_t aphase = 0, g_phase = 0;
     int unit = 0;  // ring position of the next unit, advanced exactly as the producer and the MMA thread do
     int mq = 0;
     uint32_t mq_phase = 0;
     bool ok = true;
-    auto next_acc = [&]() {
+    auto release_acc = [&](int which) {
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[ab]);
-      if (++ab == kSmallAcc) {
-        ab = 0;
-        aphase ^= 1u;
-      }
+      if (lane == 0) mbar_arrive(&acc_empty_bar[which]);
     };
-    auto load_chunk = [&](int c, uint32_t (&acc)[32]) {
+    auto load_chunk = [&](int which, int c, uint32_t (&acc)[32]) {
       __syncwarp();
-      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * 128 + c * 32),
+      tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(which * 128 + c * 32),
                     acc);
       tmem_ld_wait();
+    };
+    auto wait_acc_g = [&]() -> bool {
+      if (!mbar_wait(&acc_full_bar[kSmallAccG], g_phase)) {
+        fail(10);
+        return false;
+      }
+      g_phase ^= 1u;
+      tc_fence_after();
+      return true;
     };
     while (ok) {
       if (!mbar_wait(&mq_full_bar[mq], mq_phase)) {
@@ -353,20 +410,17 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
         mq_phase ^= 1u;
       }
       if (b < 0) break;
+      if (p.steps > 0) unit = (unit + nk) % kSmallUnits;  // the Gram pass of the input consumed nk units
       for (int it = 0; it < p.steps && ok; ++it) {
         const float ca = p.abc[3 * it], cb = p.abc[3 * it + 1], cc = p.abc[3 * it + 2];
         const bool quintic = cc != 0.0f;
         const bool last = (it == p.steps - 1);
         // ---- Gram epilogue: A (bf16) into shared memory, operand layout
-        if (!mbar_wait(&acc_full_bar[ab], aphase)) {
-          fail(10);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
+        ok = wait_acc_g();
+        if (!ok) break;
         for (int c = chunk0; c < 4; c += 2) {
           uint32_t acc[32];
-          load_chunk(c, acc);
+          load_chunk(kSmallAccG, c, acc);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             unsigned int w[4];
@@ -385,18 +439,14 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           mbar_arrive(a_ready_bar);
           if (!quintic) mbar_arrive(s_ready_bar);  // cubic step: S is A
         }
-        next_acc();
+        release_acc(kSmallAccG);
         // ---- A^2 epilogue: S = b A + c A^2 into shared memory
         if (quintic) {
-          if (!mbar_wait(&acc_full_bar[ab], aphase)) {
-            fail(10);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
+          ok = wait_acc_g();
+          if (!ok) break;
           for (int c = chunk0; c < 4; c += 2) {
             uint32_t acc[32];
-            load_chunk(c, acc);
+            load_chunk(kSmallAccG, c, acc);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const uint4 av = *reinterpret_cast<const uint4*>(a_buf + swz_offset(row, c * 32 + q * 8));
@@ -416,14 +466,13 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(s_ready_bar);
-          next_acc();
+          release_acc(kSmallAccG);
         }
         // ---- S X epilogue: X' = a X + alpha (S X), alpha = 1 (quintic) or b (cubic)
         const float alpha = quintic ? 1.0f : cb;
-        unit = (unit + nk) % kSmallUnits;  // the Gram phase consumed nk units
         for (int t = 0; t < nt && ok; ++t) {
-          const int u0 = unit, u1 = (unit + 1 == kSmallUnits) ? 0 : unit + 1;
-          unit = (u1 + 1 == kSmallUnits) ? 0 : u1 + 1;
+          const int u0 = unit, u1 = next_unit(u0);
+          unit = next_unit(u1);
           if (!mbar_wait(&acc_full_bar[ab], aphase)) {
             fail(10);
             ok = false;
@@ -435,7 +484,7 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
             const int c = chunk0 + 2 * h;  // 32-column chunk of the 128-column tile
             const int col0 = t * kSmallTileN + c * 32;
             uint32_t acc[32];
-            load_chunk(c, acc);
+            load_chunk(ab, c, acc);
             // The tile's X values sit in the ring unit the MMA just read (rows = matrix rows, 64 columns per unit,
             // 16-byte groups XOR-swizzled by the row): read a X from there, write the new iterate back in place.
             uint8_t* urow = ring + ((c < 2) ? u0 : u1) * kSmallUnitBytes + row * 128;
@@ -501,19 +550,24 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
               }
             }
           }
-          // Hand the tile (now holding the new iterate) to the store warp, then free the accumulator.
+          // Hand the tile (now holding the new iterate) to the store thread and to the Gram MMAs of the next
+          // iteration, then free the accumulator.
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&st_ready_bar[ab]);
-          next_acc();
+          if (lane == 0) mbar_arrive(&st_ready_bar[u0]);
+          release_acc(ab);
+          if (++ab == kSmallAcc) {
+            ab = 0;
+            aphase ^= 1u;
+          }
         }
       }
     }
   } else {
     // ------------------------------------------------------------------ store warp (warp 10)
     if (elect_one()) {
-      int unit = 0, sb = 0;
-      uint32_t st_bits = 0;  // phase parity of each st_ready barrier (only S X tiles complete their phases)
+      int unit = 0;
+      uint32_t st_bits = 0;  // phase parity of every st_ready barrier, as seen by this thread
       int mq = 0;
       uint32_t mq_phase = 0;
       bool ok = true;
@@ -529,28 +583,27 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
           mq_phase ^= 1u;
         }
         if (b < 0) break;
+        if (p.steps > 0) unit = (unit + nk) % kSmallUnits;  // the Gram pass of the input consumed nk units
         for (int it = 0; it < p.steps && ok; ++it) {
-          const bool quintic = p.abc[3 * it + 2] != 0.0f;
           const bool last = (it == p.steps - 1);
           const CUtensorMap* map = &maps.x[(it + 1) & 1];
-          // accumulator rotation: Gram, (A^2), then one per tile; ring rotation: nk Gram units, then two per tile
-          sb = (sb + (quintic ? 2 : 1)) % kSmallAcc;
-          unit = (unit + nk) % kSmallUnits;
           for (int t = 0; t < nt && ok; ++t) {
-            if (!mbar_wait(&st_ready_bar[sb], (st_bits >> sb) & 1u)) {
+            const int u0 = unit, u1 = next_unit(u0);
+            unit = next_unit(u1);
+            if (!mbar_wait(&st_ready_bar[u0], (st_bits >> u0) & 1u)) {
               fail(12);
               ok = false;
               break;
             }
-            st_bits ^= (1u << sb);
-            if (++sb == kSmallAcc) sb = 0;
-            const int u0 = unit, u1 = (unit + 1 == kSmallUnits) ? 0 : unit + 1;
-            unit = (u1 + 1 == kSmallUnits) ? 0 : u1 + 1;
+            st_bits ^= (1u << u0);
             if (!last) {
               tma_store_3d(map, ring + u0 * kSmallUnitBytes, t * kSmallTileN, 0, b);
               tma_store_3d(map, ring + u1 * kSmallUnitBytes, t * kSmallTileN + 64, 0, b);
               tma_store_commit();
-              tma_store_wait_read0();  // shared memory has been read: the units may be refilled
+              tma_store_wait_read0();  // shared memory has been read; the Gram MMAs give the second arrival
+            } else {
+              mbar_arrive(&empty_bar[u0]);  // nobody else reads the boxes of the last iteration
+              mbar_arrive(&empty_bar[u1]);
             }
             mbar_arrive(&empty_bar[u0]);
             mbar_arrive(&empty_bar[u1]);
