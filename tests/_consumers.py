@@ -46,7 +46,13 @@ def run_case(name, precision, device):
     init = initial_weights(cls, kw)
     params = [torch.nn.Parameter(w.clone().to(device)) for w in init]
     extra = {} if hook is None else {"weight_update_hook": getattr(hooks_pkg, hook[0])(**hook[1])}
-    opt = getattr(opt_pkg, cls)(params, fp32_matmul_prec=precision, **kw, **extra)
+    if cls == "Muown":
+        from emerging_optimizers_b200.contrib import Muown as opt_cls
+    else:
+        opt_cls = getattr(opt_pkg, cls)
+    if "betas" in kw:
+        kw = dict(kw, betas=tuple(kw["betas"]))
+    opt = opt_cls(params, fp32_matmul_prec=precision, **kw, **extra)
     got = {}
     for step in range(STEPS):
         for i, p in enumerate(params):
@@ -57,7 +63,8 @@ def run_case(name, precision, device):
                 got[f"p{i}.after{step}"] = p.detach().cpu().clone()
     for i, p in enumerate(params):
         for key, t in opt.state[p].items():
-            got[f"p{i}.{key}"] = t.detach().cpu().clone()
+            if isinstance(t, torch.Tensor):
+                got[f"p{i}.{key}"] = t.detach().cpu().clone()
     return got, init
 
 

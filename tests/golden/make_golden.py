@@ -4,6 +4,9 @@ Run once, in a container that has the reference checkout (read-only) at the path
 
     EO_REFERENCE=<reference checkout> python tests/golden/make_golden.py
 
+(add ``TORCHDYNAMO_DISABLE=1`` where the container cannot build ``torch.compile`` kernels: the reference's Muown
+decorates one elementwise helper with it, which then runs eagerly with the same arithmetic).
+
 The reference is imported, never copied.  The outputs (small .npz / .json files next to this script) are
 committed; the tests read only those files, so they also run where the reference checkout is absent.
 """
@@ -210,6 +213,11 @@ CONSUMER_CASES = {
     ),
     "muon_relative_update": ("Muon", dict(lr=0.05, momentum=0.9), ("RelativeUpdateHook", dict())),
     "mop": ("MOP", dict(lr=0.05, momentum=0.9, nesterov=True, extra_scale_factor=0.5), None),
+    "muown": (
+        "Muown",
+        dict(lr=0.05, momentum=0.9, weight_decay=0.05, betas=(0.9, 0.95), extra_scale_factor=0.2),
+        None,
+    ),
 }  # fmt: skip
 
 SPECTRAL_CASES = {
@@ -307,7 +315,11 @@ def make_consumers() -> None:
                     w = w * (kw["hyperball_radius"] / w.norm())
                 params.append(torch.nn.Parameter(w))
             extra = {} if hook is None else {"weight_update_hook": getattr(ref_hooks, hook[0])(**hook[1])}
-            opt = getattr(ref_opt, cls)(params, fp32_matmul_prec=precision, **kw, **extra)
+            if cls == "Muown":
+                from emerging_optimizers.contrib.muown import Muown as ref_cls
+            else:
+                ref_cls = getattr(ref_opt, cls)
+            opt = ref_cls(params, fp32_matmul_prec=precision, **kw, **extra)
             # Initial weights and gradients are regenerated from their seeds by the tests, not stored.
             for step in range(CONSUMER_STEPS):
                 for i, p in enumerate(params):
@@ -318,7 +330,8 @@ def make_consumers() -> None:
                         out[f"{key}.p{i}.after{step}"] = p.detach().clone().numpy()
             for i, p in enumerate(params):
                 for buf, t in opt.state[p].items():
-                    out[f"{key}.p{i}.{buf}"] = t.clone().numpy()
+                    if isinstance(t, torch.Tensor):  # Muown also keeps an integer step count
+                        out[f"{key}.p{i}.{buf}"] = t.clone().numpy()
 
     torch.set_float32_matmul_precision("highest")
     for name, (fn, shape, seed, kw) in SPECTRAL_CASES.items():
