@@ -937,6 +937,20 @@ size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }
 
 int eo_sumsq_f32_noalloc(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
                          double* sumsq, void* stream) {
+  {
+    // The first library call on a device resolves symbol addresses and sets kernel attributes, which is not
+    // allowed while a stream is being captured: refuse that combination instead of failing inside the set-up.
+    int cur = 0;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur >= 0 && cur < kMaxDevices &&
+        cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap) == cudaSuccess &&
+        cap != cudaStreamCaptureStatusNone) {
+      std::lock_guard<std::mutex> lock(g_mu);
+      if (!g_dev[cur].ready)
+        return fail(EO_ERR_BAD_ARG, "eo_sumsq_f32_noalloc: the first library call on a device must be made outside "
+                                    "stream capture");
+    }
+  }
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");

@@ -153,6 +153,9 @@ class Muon(OrthogonalizedOptimizer[HookStateT]):
             and self._coefficient_type in muon_utils._COEFFICIENT_SETS
             and cls.orthogonalize is base.orthogonalize
             and cls._step_param is base._step_param
+            and cls._momentum_update is base._momentum_update
+            and cls._init_group is base._init_group
+            and cls._apply_weight_decay_inplace is base._apply_weight_decay_inplace
             and cls.pre_weight_update_fn_inplace is base.pre_weight_update_fn_inplace
             and cls.post_weight_update_fn_inplace is base.post_weight_update_fn_inplace
             and type(self._weight_update_hook) is NoOpWeightUpdateHook
@@ -167,7 +170,10 @@ class Muon(OrthogonalizedOptimizer[HookStateT]):
         Parameters that the fused kernels can take (2-D contiguous fp32 CUDA tensors, bf16 path, no customised
         hook or override) are processed as groups of equally shaped matrices: fused momentum / normalise kernels,
         one batched Newton-Schulz run per group, fused weight update.  Everything else takes the per-parameter
-        path of the base class.  Both paths compute the same update.
+        path of the base class.  Both paths compute the same update.  One visible difference: with
+        ``weight_decay_method="l2"`` the per-parameter path adds ``weight_decay * p`` into ``p.grad`` in place (as the
+        reference does), while the fused kernels form ``g + weight_decay * p`` on the fly and leave ``p.grad`` as the
+        caller set it.
         """
         if closure is not None:
             raise ValueError("closure is not supported")
