@@ -76,7 +76,7 @@ _PROTOTYPES: dict[str, tuple] = {
     "eo_muon_prepare_batch": (
         c_int,
         [c_int, c_void_p, c_void_p, c_void_p, c_int64, c_double, c_int, c_float, c_float, c_void_p, c_int64]
-        + [c_void_p, c_void_p, c_size_t, c_void_p],
+        + [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p],
     ),
     "eo_muon_apply_batch": (
         c_int,
@@ -86,7 +86,12 @@ _PROTOTYPES: dict[str, tuple] = {
     "eo_newton_schulz_bf16": (
         c_int,
         [c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_void_p, c_int, c_int]
-        + [c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p],
+        + [c_void_p, c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
+    "eo_cast_sumsq_f32": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, c_float]
+        + [c_void_p, c_void_p, c_void_p, c_size_t, c_void_p],
     ),
     "eo_newton_schulz_f32_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "eo_newton_schulz_f32": (
@@ -484,24 +489,31 @@ def _ptr_array(tensors) -> "ctypes.Array":
 
 
 def muon_prepare_batch(
-    grads, momenta, params, momentum: float, nesterov: bool, l2: float, eps: float, out_stack: torch.Tensor
-) -> torch.Tensor:
+    grads, momenta, params, momentum: float, nesterov: bool, l2: float, eps: float, out_stack: torch.Tensor,
+    scales: torch.Tensor | None = None,
+) -> torch.Tensor:  # fmt: skip
     """Momentum update of ``n`` equally sized flat-contiguous fp32 tensors and their normalised bf16 images written
-    to ``out_stack[i]``; returns the float64 sums of squares (n,).  See ``eo_muon_prepare_batch``."""
+    to ``out_stack[i]``; returns the float64 sums of squares (n,).  With ``scales`` (fp32, shape (n, 2)) the division
+    is deferred: ``out_stack[i]`` receives the un-normalised update and ``scales[i]`` the factors that
+    :func:`newton_schulz_bf16` applies.  See ``eo_muon_prepare_batch``."""
     n = len(grads)
     dev = grads[0].device
     numel = grads[0].numel()
     assert out_stack.dtype == torch.bfloat16 and out_stack.is_contiguous() and out_stack.size(0) == n
     slot_stride = out_stack[0].numel()
     assert slot_stride >= numel and slot_stride % 8 == 0
+    if scales is not None:
+        assert scales.dtype == torch.float32 and scales.is_contiguous() and scales.numel() == 2 * n
     ss = torch.empty(n, dtype=torch.float64, device=dev)
     nbytes = lib().eo_muon_prepare_scratch_bytes(n, numel)
     scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev), _Timed("muon_prepare", 3 * ((n + 47) // 48), dev):
+    launches = (2 if scales is not None else 3) * ((n + 47) // 48)
+    with torch.cuda.device(dev), _Timed("muon_prepare", launches, dev):
         rc = lib().eo_muon_prepare_batch(
             n, _ptr_array(grads), _ptr_array(momenta), _ptr_array(params) if l2 != 0.0 else None, numel,
             momentum, 1 if nesterov else 0, l2, eps, out_stack.data_ptr(), slot_stride,
-            ss.data_ptr(), scratch.data_ptr(), nbytes, torch.cuda.current_stream(dev).cuda_stream,
+            ss.data_ptr(), scales.data_ptr() if scales is not None else None, scratch.data_ptr(), nbytes,
+            torch.cuda.current_stream(dev).cuda_stream,
         )  # fmt: skip
     _check(rc, "eo_muon_prepare_batch")
     return ss
@@ -530,11 +542,36 @@ def muon_apply_batch(
 FUSED_SMALL_MATRICES = True
 
 
+def cast_sumsq(x: torch.Tensor, eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """One pass over a row-major fp32 ``x`` ((B,) rows, cols): its bf16 image (un-normalised, dense) and the
+    per-matrix factors ``[1 / norm^2, 1 / norm]`` (fp32, shape (B, 2)) that :func:`newton_schulz_bf16` applies in
+    its first two epilogues instead of a normalisation pass.  See ``eo_cast_sumsq_f32``."""
+    require_cuda(x, "x")
+    assert x.dtype == torch.float32
+    batch = x.size(0) if x.dim() == 3 else 1
+    mn, ld, bs = _mat_layout(x)
+    assert mn == 0, "x must be row-major"
+    rows, cols = x.size(-2), x.size(-1)
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    scales = torch.empty((batch, 2), dtype=torch.float32, device=x.device)
+    nbytes = lib().eo_sumsq_scratch_bytes(batch, rows, cols)
+    scratch = torch.empty(max(nbytes, 8), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device), _Timed("cast_sumsq", 2, x.device):
+        rc = lib().eo_cast_sumsq_f32(
+            x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, out.data_ptr(), cols, rows * cols,
+            eps, None, scales.data_ptr(), scratch.data_ptr(), nbytes, _stream(x),
+        )  # fmt: skip
+    _check(rc, "eo_cast_sumsq_f32")
+    return out, scales
+
+
 def newton_schulz_bf16(
-    x: torch.Tensor, schedule, use_syrk: bool, out_dtype: torch.dtype = torch.bfloat16
-) -> torch.Tensor:
-    """Run the whole iteration loop on a normalised bf16 iterate ``x`` ((B,) rows, cols, row-major, 16-byte
-    aligned rows) with one library call; ``x`` is clobbered.  Returns a new contiguous tensor of ``out_dtype``."""
+    x: torch.Tensor, schedule, use_syrk: bool, out_dtype: torch.dtype = torch.bfloat16,
+    scales: torch.Tensor | None = None,
+) -> torch.Tensor:  # fmt: skip
+    """Run the whole iteration loop on a bf16 iterate ``x`` ((B,) rows, cols, row-major, 16-byte aligned rows) with
+    one library call; ``x`` is clobbered.  ``x`` is the normalised input, or, with ``scales`` from
+    :func:`cast_sumsq`, its un-normalised image.  Returns a new contiguous tensor of ``out_dtype``."""
     require_cuda(x, "x")
     assert x.dtype == torch.bfloat16 and len(schedule) >= 1
     batch = x.size(0) if x.dim() == 3 else 1
@@ -556,7 +593,7 @@ def newton_schulz_bf16(
             x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
             (1 if use_syrk else 0) | (0 if FUSED_SMALL_MATRICES else 2),
             out.data_ptr(), 1 if out_dtype == torch.float32 else 0, cols, rows * cols,
-            ws.data_ptr(), nbytes, _stream(x),
+            ws.data_ptr(), nbytes, scales.data_ptr() if scales is not None else None, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_bf16")
     return out

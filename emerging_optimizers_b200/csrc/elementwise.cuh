@@ -124,6 +124,64 @@ __global__ void __launch_bounds__(kEwThreads)
   }
 }
 
+// One pass over an fp32 matrix batch that writes it rounded to bf16 (NOT normalised) and leaves per-block partial
+// sums of squares of the fp32 values: the first half of a Frobenius normalisation whose division is applied later,
+// inside the epilogues of the first Gram and the first update product (see GemmParams::dev_scale).
+__global__ void __launch_bounds__(kEwThreads)
+    cast_sumsq_kernel(const float* __restrict__ x, long long rows, long long cols, long long ld, long long stride,
+                      unsigned short* __restrict__ out, long long ldo, long long strideo, int vec4,
+                      double* __restrict__ partial) {
+  const int b = blockIdx.y;
+  const float* xb = x + static_cast<long long>(b) * stride;
+  unsigned short* ob = out + static_cast<long long>(b) * strideo;
+  double acc = 0.0;
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  if (vec4) {
+    const long long c4 = cols >> 2;
+    const long long units = rows * c4;
+    for (long long u = tid; u < units; u += nthreads) {
+      const long long r = u / c4, c = u - r * c4;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(xb + r * ld) + c);
+      acc += static_cast<double>(v.x) * v.x + static_cast<double>(v.y) * v.y;
+      acc += static_cast<double>(v.z) * v.z + static_cast<double>(v.w) * v.w;
+      uint2 t;
+      t.x = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v.x))) |
+            (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v.y))) << 16);
+      t.y = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v.z))) |
+            (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(v.w))) << 16);
+      reinterpret_cast<uint2*>(ob + r * ldo)[c] = t;
+    }
+  } else {
+    const long long units = rows * cols;
+    for (long long u = tid; u < units; u += nthreads) {
+      const long long r = u / cols, c = u - r * cols;
+      const float v = xb[r * ld + c];
+      acc += static_cast<double>(v) * v;
+      ob[r * ldo + c] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    }
+  }
+  const double total = block_reduce_sum(acc);
+  if (threadIdx.x == 0) partial[static_cast<long long>(b) * gridDim.x + blockIdx.x] = total;
+}
+
+// sumsq[b] as in sumsq_final_kernel, plus the two factors the deferred normalisation needs:
+// scales[2 b] = 1 / max(norm, eps)^2 (for X X^T) and scales[2 b + 1] = 1 / max(norm, eps) (for X itself).
+__global__ void __launch_bounds__(kEwThreads)
+    sumsq_scales_kernel(const double* __restrict__ partial, int nblk, float eps, double* __restrict__ sumsq,
+                        float* __restrict__ scales) {
+  const int b = blockIdx.x;
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < nblk; i += kEwThreads) acc += partial[static_cast<long long>(b) * nblk + i];
+  const double total = block_reduce_sum(acc);
+  if (threadIdx.x == 0) {
+    if (sumsq != nullptr) sumsq[b] = total;
+    const float inv = 1.0f / fmaxf(static_cast<float>(sqrt(total)), eps);
+    scales[2 * b] = inv * inv;
+    scales[2 * b + 1] = inv;
+  }
+}
+
 // Split fp32 into three bf16 planes with x = p0 + p1 + p2 up to 2^-24 relative: p0 = bf16(x),
 // p1 = bf16(x - p0), p2 = bf16(x - p0 - p1); both remainders are exact in fp32.
 __global__ void __launch_bounds__(kEwThreads)
@@ -289,6 +347,69 @@ __device__ __forceinline__ void muon_momentum_body(const float* __restrict__ g, 
   if (threadIdx.x == 0) *partial_slot = total;
 }
 
+// Pass 1 with the update written out: as muon_momentum_body, plus u itself rounded to bf16 (NOT normalised) into
+// `out`.  With the division deferred to the epilogues of the first two products of the iteration (see
+// GemmParams::dev_scale) this is the only elementwise pass before Newton-Schulz: g and m are read once.
+__device__ __forceinline__ void muon_momentum_cast_body(const float* __restrict__ g, float* __restrict__ m,
+                                                        const float* __restrict__ p, long long numel, const MuonEw& c,
+                                                        __nv_bfloat16* __restrict__ out,
+                                                        double* __restrict__ partial_slot) {
+  double acc = 0.0;
+  const long long tid = static_cast<long long>(blockIdx.x) * kEwThreads + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * kEwThreads;
+  const long long n4 = numel >> 2;
+  const float4* g4 = reinterpret_cast<const float4*>(g);
+  const float4* p4 = reinterpret_cast<const float4*>(p);
+  float4* m4 = reinterpret_cast<float4*>(m);
+  const bool l2 = c.l2 != 0.0f;
+  const float w = c.one_minus_momentum;
+  auto quad = [&](float4 gv, float4& mv, long long i) {
+    mv.x = lerp_f32(mv.x, gv.x, w); mv.y = lerp_f32(mv.y, gv.y, w);
+    mv.z = lerp_f32(mv.z, gv.z, w); mv.w = lerp_f32(mv.w, gv.w, w);
+    const float u0 = muon_update(gv.x, mv.x, c), u1 = muon_update(gv.y, mv.y, c);
+    const float u2 = muon_update(gv.z, mv.z, c), u3 = muon_update(gv.w, mv.w, c);
+    uint2 t;
+    t.x = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(u0))) |
+          (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(u1))) << 16);
+    t.y = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(u2))) |
+          (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(u3))) << 16);
+    reinterpret_cast<uint2*>(out)[i] = t;
+    const double d0 = u0, d1 = u1, d2 = u2, d3 = u3;
+    return (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+  };
+  long long i = tid;
+  for (; i + nthreads < n4; i += 2 * nthreads) {  // two grid strides per trip, loads first (see muon_momentum_body)
+    float4 g0 = __ldg(g4 + i), g1 = __ldg(g4 + i + nthreads);
+    float4 m0 = m4[i], m1 = m4[i + nthreads];
+    if (l2) {
+      g0 = muon_add_l2(g0, __ldg(p4 + i), c.l2);
+      g1 = muon_add_l2(g1, __ldg(p4 + i + nthreads), c.l2);
+    }
+    acc += quad(g0, m0, i);
+    m4[i] = m0;
+    acc += quad(g1, m1, i + nthreads);
+    m4[i + nthreads] = m1;
+  }
+  for (; i < n4; i += nthreads) {
+    float4 gv = __ldg(g4 + i);
+    float4 mv = m4[i];
+    if (l2) gv = muon_add_l2(gv, __ldg(p4 + i), c.l2);
+    acc += quad(gv, mv, i);
+    m4[i] = mv;
+  }
+  for (long long j = (n4 << 2) + tid; j < numel; j += nthreads) {
+    float gv = g[j];
+    if (l2) gv = __fmaf_rn(c.l2, p[j], gv);
+    const float mv = lerp_f32(m[j], gv, w);
+    m[j] = mv;
+    const float u = muon_update(gv, mv, c);
+    out[j] = __float2bfloat16_rn(u);
+    acc += static_cast<double>(u) * u;
+  }
+  const double total = block_reduce_sum(acc);
+  if (threadIdx.x == 0) *partial_slot = total;
+}
+
 // Pass 2: recompute u from g and the updated momentum buffer, divide by the norm, write bf16.
 __device__ __forceinline__ void muon_normalize_body(const float* __restrict__ g, const float* __restrict__ m,
                                                     const float* __restrict__ p, long long numel, const MuonEw& c,
@@ -418,6 +539,15 @@ __global__ void __launch_bounds__(kEwThreads)
   muon_normalize_body(t.g[y], t.m[y], t.p[y], numel, c, sumsq[y], eps, out + static_cast<long long>(y) * slot_stride);
 }
 
+__global__ void __launch_bounds__(kEwThreads)
+    muon_momentum_cast_mt_kernel(const __grid_constant__ MtPrepare t, long long numel, MuonEw c,
+                                 __nv_bfloat16* __restrict__ out, long long slot_stride,
+                                 double* __restrict__ partial) {
+  const int y = blockIdx.y;
+  muon_momentum_cast_body(t.g[y], t.m[y], t.p[y], numel, c, out + static_cast<long long>(y) * slot_stride,
+                          partial + static_cast<long long>(y) * gridDim.x + blockIdx.x);
+}
+
 template <typename U>
 __global__ void __launch_bounds__(kEwThreads)
     muon_apply_mt_kernel(const __grid_constant__ MtApply t, float shrink, float extra, float lr) {
@@ -444,6 +574,22 @@ inline void launch_sumsq(const float* x, int batch, int64_t rows, int64_t cols, 
                                                                     scratch + static_cast<long long>(b0) * nblk);
   }
   sumsq_final_kernel<<<batch, kEwThreads, 0, stream>>>(scratch, nblk, sumsq);
+}
+
+inline void launch_cast_sumsq(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                              void* out, int64_t ldo, int64_t strideo, float eps, double* sumsq, float* scales,
+                              double* scratch, cudaStream_t stream) {
+  const int nblk = sumsq_blocks_per_matrix(rows, cols);
+  const int vec4 = (cols % 4 == 0) && (ld % 4 == 0) && (stride % 4 == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                   (reinterpret_cast<uintptr_t>(out) % 8 == 0) && (ldo % 4 == 0) && (strideo % 4 == 0);
+  for (int b0 = 0; b0 < batch; b0 += 65535) {
+    const int nb = (batch - b0 < 65535) ? (batch - b0) : 65535;
+    cast_sumsq_kernel<<<dim3(nblk, nb), kEwThreads, 0, stream>>>(
+        x + static_cast<long long>(b0) * stride, rows, cols, ld, stride,
+        static_cast<unsigned short*>(out) + static_cast<long long>(b0) * strideo, ldo, strideo, vec4,
+        scratch + static_cast<long long>(b0) * nblk);
+  }
+  sumsq_scales_kernel<<<batch, kEwThreads, 0, stream>>>(scratch, nblk, eps, sumsq, scales);
 }
 
 inline void launch_normalize(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,

@@ -155,7 +155,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
                 int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
                 int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
                 int round_bf16, int tri, int skip_upper, void* stream, const TpExchange* tp = nullptr,
-                int d_multicast = 0) {
+                int d_multicast = 0, const float* dev_scale = nullptr, int dev_scale_mode = 0) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(EO_ERR_BAD_ARG, "negative size");
@@ -229,6 +229,8 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   p.beta = beta;
   p.post_scale = post_scale;
   p.status = dev->status_ptr;
+  p.dev_scale = dev_scale;
+  p.dev_scale_mode = dev_scale_mode;
 
   // Descriptor geometry.  K-major: rows of 128 bytes along K, eight-row groups 1024 bytes apart,
   // each MMA consumes 32 bytes of a row.  MN-major: rows of 128 bytes along M/N (one per k),
@@ -449,6 +451,25 @@ int eo_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t 
   return EO_OK;
 }
 
+int eo_cast_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride, void* out_bf16,
+                      int64_t ldo, int64_t strideo, float eps, double* sumsq, float* scales, void* scratch,
+                      size_t scratch_bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (batch < 0 || rows < 0 || cols < 0) return fail(EO_ERR_BAD_ARG, "negative size");
+  if (batch == 0) return EO_OK;
+  if (scales == nullptr || out_bf16 == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (ld < cols || ldo < cols) return fail(EO_ERR_BAD_ARG, "leading dimension smaller than cols");
+  const size_t need = eo_sumsq_scratch_bytes(batch, rows, cols);
+  if (scratch_bytes < need || (need > 0 && scratch == nullptr))
+    return fail(EO_ERR_WORKSPACE, "cast_sumsq scratch: need %zu bytes, got %zu", need, scratch_bytes);
+  if (rows > 0 && cols > 0 && x == nullptr) return fail(EO_ERR_BAD_ARG, "x is NULL");
+  eo::launch_cast_sumsq(x, batch, rows, cols, ld, stride, out_bf16, ldo, strideo, eps, sumsq, scales,
+                        static_cast<double*>(scratch), static_cast<cudaStream_t>(stream));
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
 size_t eo_muon_scratch_bytes(int64_t numel) {
   if (numel <= 0) return 0;
   return static_cast<size_t>(eo::sumsq_blocks_per_matrix(numel, 1)) * sizeof(double);
@@ -520,7 +541,8 @@ size_t eo_muon_prepare_scratch_bytes(int n, int64_t numel) {
 
 int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const float* const* p, int64_t numel,
                           double momentum, int nesterov, float l2_weight_decay, float eps, void* out_stack,
-                          int64_t slot_stride, double* sumsq, void* scratch, size_t scratch_bytes, void* stream) {
+                          int64_t slot_stride, double* sumsq, float* dev_scales, void* scratch, size_t scratch_bytes,
+                          void* stream) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (n < 0 || numel < 0) return fail(EO_ERR_BAD_ARG, "negative size");
@@ -552,6 +574,15 @@ int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const f
       t.g[i] = g[i0 + i];
       t.m[i] = m[i0 + i];
       t.p[i] = (p != nullptr) ? p[i0 + i] : nullptr;
+    }
+    if (dev_scales != nullptr) {
+      // deferred normalisation: one pass writes the un-normalised bf16 update; the iteration applies the factors
+      eo::muon_momentum_cast_mt_kernel<<<dim3(nblk, cnt), eo::kEwThreads, 0, s>>>(
+          t, numel, c, static_cast<__nv_bfloat16*>(out_stack) + static_cast<int64_t>(i0) * slot_stride, slot_stride,
+          partial + static_cast<int64_t>(i0) * nblk);
+      eo::sumsq_scales_kernel<<<cnt, eo::kEwThreads, 0, s>>>(partial + static_cast<int64_t>(i0) * nblk, nblk, eps,
+                                                             sumsq + i0, dev_scales + 2 * static_cast<int64_t>(i0));
+      continue;
     }
     eo::muon_momentum_mt_kernel<<<dim3(nblk, cnt), eo::kEwThreads, 0, s>>>(t, numel, c,
                                                                           partial + static_cast<int64_t>(i0) * nblk);
@@ -672,7 +703,7 @@ int launch_ns_small(DeviceInfo* dev, void* X, int batch, int rows, int cols, int
 
 int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
                           int steps, int flags, void* out, int out_fp32, int64_t ldo, int64_t strideo,
-                          void* workspace, size_t workspace_bytes, void* stream) {
+                          void* workspace, size_t workspace_bytes, const float* dev_scales, void* stream) {
   const int use_syrk = flags & 1;
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
@@ -693,7 +724,10 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
   const int syrk = use_syrk && (rows % 8 == 0) && (cols % 8 == 0);
 
   // Matrices whose Gram matrix is a single tile take the fused kernel: A, A^2 and S stay in shared memory.
-  if (!(flags & 2) && rows <= 128 && rows <= cols && cols >= 256 && steps <= eo::kSmallMaxSteps)
+  const bool small = !(flags & 2) && rows <= 128 && rows <= cols && cols >= 256 && steps <= eo::kSmallMaxSteps;
+  if (small && dev_scales != nullptr)
+    return fail(EO_ERR_BAD_ARG, "deferred normalisation (dev_scales) is not available for matrices of up to 128 rows");
+  if (small)
     return launch_ns_small(dev, X, batch, rows, cols, ld, stride, host_abc, steps, T, L.ldt, L.t_stride, out, out_fp32,
                            ldo, strideo, stream);
 
@@ -705,8 +739,12 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
     const bool last = (it == steps - 1);
     int rc;
     // A = X X^T over the wide orientation.  Wide storage: operands K-major; tall storage: MN-major.
+    // With deferred normalisation the first iterate is un-normalised: its Gram product takes 1 / norm^2 and its
+    // update 1 / norm from the device, after which the iterate is what the normalised input would have given.
+    const float* ds = (it == 0) ? dev_scales : nullptr;
     rc = launch_gemm(cur, tall ? 1 : 0, cur_ld, cur_stride, 0, cur, tall ? 1 : 0, cur_ld, cur_stride, 0, nullptr, 0, 0,
-                     A, L.ldm, a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 0, 0, 0, syrk, 0, stream);
+                     A, L.ldm, a_stride, batch, L.m, L.m, L.n, 1.0f, 0.0f, 1.0f, 0, 0, 0, syrk, 0, stream, nullptr, 0,
+                     ds, 1);
     if (rc) return rc;
     const void* Sop = A;
     float alpha = b, beta = a;
@@ -734,11 +772,11 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
     if (!tall) {
       // X' = beta X + alpha S X : A-operand S (m x m, K-major), B-operand X as (n x m): stored m x n, MN-major
       rc = launch_gemm(Sop, 0, L.ldm, a_stride, 0, cur, 1, cur_ld, cur_stride, 0, cur, cur_ld, cur_stride, dst, dst_ld,
-                       dst_stride, batch, L.m, L.n, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream);
+                       dst_stride, batch, L.m, L.n, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream, nullptr, 0, ds, 2);
     } else {
       // stored transposed (n x m): X'^T = beta X^T + alpha X^T S, S symmetric, both operands K-major
       rc = launch_gemm(cur, 0, cur_ld, cur_stride, 0, Sop, 0, L.ldm, a_stride, 0, cur, cur_ld, cur_stride, dst, dst_ld,
-                       dst_stride, batch, L.n, L.m, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream);
+                       dst_stride, batch, L.n, L.m, L.m, alpha, beta, 1.0f, 0, d32, d32, 0, 0, stream, nullptr, 0, ds, 2);
     }
     if (rc) return rc;
     cur = dst;

@@ -113,6 +113,11 @@ struct GemmParams {
   long long tp_wait_cycles;         // budget of one wait for the other ranks' flags
   // D is a multicast address (general product, bf16 D, N a multiple of 32): every store goes to all ranks.
   int d_mc;
+  // Deferred Frobenius normalisation: per-matrix factors on the device (two floats per batch entry, see
+  // sumsq_scales_kernel).  Mode 1 multiplies alpha by dev_scale[2 b] (the product of two un-normalised operands);
+  // mode 2 multiplies alpha * acc + beta * C by dev_scale[2 b + 1] before the result is rounded.
+  const float* dev_scale;
+  int dev_scale_mode;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
@@ -153,7 +158,7 @@ __device__ __forceinline__ float bf16_bits_to_float(unsigned short h) {
 
 // Epilogue for one 32-column chunk held by one thread (row `row`, columns col0..col0+31).
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], long long batch_c,
-                                               long long batch_d, int row, int col0) {
+                                               long long batch_d, int row, int col0, float alpha, float sum_scale) {
   if (row >= p.M) return;
   const bool has_c = (p.beta != 0.0f) && (p.C != nullptr);
   const int ncols = min(32, p.N - col0);
@@ -162,7 +167,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   const int ndirect = p.tri ? max(0, min(ncols, row - col0 + 1)) : ncols;
   float v[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = p.alpha * __uint_as_float(acc[j]);
+  for (int j = 0; j < 32; ++j) v[j] = alpha * __uint_as_float(acc[j]);
 
   const bool full = (ndirect == 32);
   if (has_c) {
@@ -202,6 +207,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
           if (j < ndirect) v[j] = fmaf(p.beta, bf16_bits_to_float(c[j]), v[j]);
       }
     }
+  }
+
+  if (sum_scale != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= sum_scale;
   }
 
   if (p.d_fp32) {
@@ -547,6 +557,13 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
       const long long batch_c = static_cast<long long>(b) * p.strideC;
       const long long batch_d = static_cast<long long>(b) * p.strideD;
       const int nchunks = p.bn / 32;
+      float alpha = p.alpha, sum_scale = 1.0f;
+      if (p.dev_scale != nullptr) {
+        if (p.dev_scale_mode == 1)
+          alpha *= __ldg(p.dev_scale + 2 * b);
+        else
+          sum_scale = __ldg(p.dev_scale + 2 * b + 1);
+      }
       if (kTp) {
         // Write the partial tile into this rank's buffer, then let the last warp working on this accumulator raise
         // the flag at the tile's owner.  Owners and slots are defined on the 128-row tile grid; a 256-row tile is
@@ -596,7 +613,7 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
                             static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
                         acc);
           tmem_ld_wait();
-          epilogue_chunk(p, acc, batch_c, batch_d, row, col0);
+          epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
         }
       }
       tc_fence_before();

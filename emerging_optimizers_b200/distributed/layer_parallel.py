@@ -29,6 +29,7 @@ Design for one NVSwitch box (one process per GPU, NCCL through ``torch.distribut
 
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass, field
 from typing import Sequence
 
@@ -77,21 +78,30 @@ class _Bucket:
     slot_numel: int = 0
 
 
-def _plan_buckets(numels: Sequence[int], owners: Sequence[int], world: int, bucket_numel: int) -> list[_Bucket]:
-    """Cut every rank's owned list into consecutive groups; group j of all ranks forms bucket j.
+def _plan_buckets(
+    numels: Sequence[int], owners: Sequence[int], world: int, bucket_numel: int, shapes: Sequence[tuple] | None = None
+) -> list[_Bucket]:
+    """Cut every rank's owned list into groups; group j of all ranks forms bucket j.
 
-    A group is closed once it holds ``bucket_numel`` elements.  The slot size of a bucket is the largest group in
-    it (rounded up to 8 elements), so the all-gather has equal-sized slots.
+    A group is closed once it holds ``bucket_numel`` elements.  With ``shapes`` a rank's list is first ordered by
+    shape, largest matrices first, and a group is also closed where the shape changes: every group is then a stack
+    of equally shaped matrices, i.e. one batched Newton-Schulz run, and the last buckets (whose exchange nothing
+    is left to hide behind) hold the smallest matrices.  Without ``shapes`` the list stays in index order.  The slot
+    size of a bucket is the largest group in it (rounded up to 8 elements), so the all-gather has equal-sized slots.
     """
     owned: list[list[int]] = [[] for _ in range(world)]
     for i, r in enumerate(owners):
         owned[r].append(i)
+    if shapes is not None:
+        for r in range(world):
+            owned[r].sort(key=lambda i: (-numels[i], tuple(shapes[i]), i))
     groups: list[list[list[tuple[int, int]]]] = []
     for r in range(world):
         mine: list[list[tuple[int, int]]] = [[]]
         fill = 0
         for i in owned[r]:
-            if fill >= bucket_numel and mine[-1]:
+            new_shape = shapes is not None and mine[-1] and tuple(shapes[mine[-1][-1][0]]) != tuple(shapes[i])
+            if (fill >= bucket_numel or new_shape) and mine[-1]:
                 mine.append([])
                 fill = 0
             mine[-1].append((i, fill))
@@ -123,7 +133,8 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         params: the 2-D parameters (or parameter groups), in the same order on every rank.
         group: process group to divide the work over (``None``: the default group; a single process if
             torch.distributed is not initialised).
-        bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier.
+        bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier, larger ones
+            give the batched Newton-Schulz runs more matrices per launch.  A bucket holds matrices of one shape.
         exchange_dtype: dtype of the gathered updates.  ``None`` picks bf16 on the "medium" path (lossless there)
             and fp32 otherwise.
         exchange: "updates": all-gather the orthogonalized updates, every rank applies all of them.
@@ -177,7 +188,9 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         self.exchange_dtype = exchange_dtype or (torch.bfloat16 if fp32_matmul_prec == "medium" else torch.float32)
 
         self.owners = partition_by_cost([ns_cost(p.shape) for p in self.params], self.world)
-        self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel)
+        self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel,
+                                     [tuple(p.shape) for p in self.params])  # fmt: skip
+        self._ns_streams: list = []  # two streams the buckets' Newton-Schulz work alternates between (GPU ranks)
         self._side: "torch.cuda.Stream | None" = None
         self._peer = None  # symmetric exchange buffer, created collectively at the first multi-GPU step
         self._param_peer = None  # exchange="parameters": the symmetric buffer the parameters live in
@@ -208,6 +221,25 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         for i in idxs:
             runs.setdefault(id(self._group_of[i]), []).append(i)
         return list(runs.values())
+
+    def _fork_compute_streams(self, dev: torch.device) -> list:
+        """Two streams, made to wait for everything enqueued on the current stream so far.  The Newton-Schulz work
+        of consecutive buckets alternates between them: each product is a persistent launch whose last wave leaves
+        SMs idle, and with an independent chain of launches in flight those SMs pick up the other bucket's tiles."""
+        if dev.type != "cuda":
+            return []
+        if not self._ns_streams:
+            self._ns_streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+        fork = torch.cuda.Event()
+        fork.record(torch.cuda.current_stream(dev))
+        for s in self._ns_streams:
+            s.wait_event(fork)
+        return self._ns_streams
+
+    def _join_compute_streams(self, dev: torch.device) -> None:
+        cur = torch.cuda.current_stream(dev)
+        for s in self._ns_streams:
+            cur.wait_stream(s)
 
     def _orthogonalize_owned(self, i: int) -> torch.Tensor:
         """Momentum update, Nesterov and Newton-Schulz for parameter ``i`` (owned by this rank); unscaled."""
@@ -287,14 +319,18 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             if p.grad is None:
                 raise RuntimeError(f"parameter {i} has no gradient; layer-parallel Muon needs all gradients")
         fused = self._use_fused_kernels()
+        dev = self.params[0].device
         if self.world == 1:
-            for b in self.buckets:
+            streams = self._fork_compute_streams(dev) if fused else []
+            for j, b in enumerate(self.buckets):
                 idxs = [i for i, _ in b.per_rank[0]]
-                orths = self._orthogonalize_many(idxs, fused)
-                self._apply_many(idxs, [orths[i] for i in idxs], fused)
+                with torch.cuda.stream(streams[j % 2]) if streams else contextlib.nullcontext():
+                    orths = self._orthogonalize_many(idxs, fused)
+                    self._apply_many(idxs, [orths[i] for i in idxs], fused)
+            if streams:
+                self._join_compute_streams(dev)
             return
 
-        dev = self.params[0].device
         if self.exchange == "parameters":
             self._step_exchanging_parameters(fused, dev)
             return
@@ -324,13 +360,15 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             self._peer = PeerBuffer(2 * self.world * max_slot, self.exchange_dtype, dev, self.group)
             self._exchanges = 0
         peer, side = self._peer, self._side
-        for b in self.buckets:
+        streams = self._fork_compute_streams(dev)
+        for j, b in enumerate(self.buckets):
             mine = b.per_rank[self.rank]
-            orths = self._orthogonalize_many([i for i, _ in mine], fused)
+            with torch.cuda.stream(streams[j % 2]):
+                orths = self._orthogonalize_many([i for i, _ in mine], fused)
+                ready = torch.cuda.Event()
+                ready.record()
             base = (self._exchanges % 2) * self.world * max_slot
             self._exchanges += 1
-            ready = torch.cuda.Event()
-            ready.record()
             with torch.cuda.stream(side):
                 side.wait_event(ready)
                 own = base + self.rank * b.slot_numel
@@ -339,6 +377,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
                     orths[i].record_stream(side)
                 peer.all_gather_slots(base, b.slot_numel)
                 self._apply_bucket(b, peer.local[base : base + self.world * b.slot_numel], fused)
+        self._join_compute_streams(dev)
         torch.cuda.current_stream().wait_stream(side)
 
     # -- exchange="parameters" ---------------------------------------------------------------------------
@@ -401,15 +440,18 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         # Entry barrier: a peer may write my copy of its matrices only after everything I enqueued before this step
         # (the backward pass that read them) is done, and symmetrically.
         peer.barrier()
-        for b, base in zip(self.buckets, self._bucket_bases()):
+        streams = self._fork_compute_streams(dev)
+        for j, (b, base) in enumerate(zip(self.buckets, self._bucket_bases())):
             mine = [i for i, _ in b.per_rank[self.rank]]
-            orths = self._orthogonalize_many(mine, fused)
-            self._apply_many(mine, [orths[i] for i in mine], fused)
-            ready = torch.cuda.Event()
-            ready.record()
+            with torch.cuda.stream(streams[j % 2]):
+                orths = self._orthogonalize_many(mine, fused)
+                self._apply_many(mine, [orths[i] for i in mine], fused)
+                ready = torch.cuda.Event()
+                ready.record()
             with torch.cuda.stream(side):
                 side.wait_event(ready)
                 peer.all_gather_slots(base, b.slot_numel)
+        self._join_compute_streams(dev)
         torch.cuda.current_stream().wait_stream(side)
 
     def _apply_bucket(self, b: _Bucket, gathered: torch.Tensor, fused: bool) -> None:

@@ -27,6 +27,22 @@ from emerging_optimizers_b200.orthogonalized_optimizers import muon_utils
 # Upper bound on the bf16 bytes of one stacked batch (keeps A, B and the two iterates of a batch near 3 GiB).
 MAX_BATCH_BYTES = 1 << 30
 
+# Batches (groups of equally shaped matrices) are issued round-robin on this many CUDA streams.  Every product of a
+# batch is a persistent launch whose last wave leaves SMs idle (a k/v-sized group of a sharded model has fewer tiles
+# than the GPU has SMs); with a second, independent chain of launches in flight those SMs pick up the other chain's
+# CTAs, and the tile scheduler of the kernels shares the machine between the two.  Results do not depend on it.
+# 1 issues everything on the caller's stream.
+NS_STREAMS = 2
+
+_side_streams: dict[tuple, list] = {}
+
+
+def _streams(device: torch.device, n: int) -> list:
+    key = (device.index, n)
+    if key not in _side_streams:
+        _side_streams[key] = [torch.cuda.Stream(device=device) for _ in range(n)]
+    return _side_streams[key]
+
 
 def eligible(p: torch.Tensor, g: torch.Tensor | None) -> bool:
     """True if the fused kernels can take this parameter: 2-D fp32 CUDA, contiguous, gradient likewise."""
@@ -90,7 +106,9 @@ def orthogonalized_updates(
     schedule = list(muon_utils.get_coefficient_iterator(steps, sets, mode=mode))
 
     out: list[torch.Tensor | None] = [None] * len(params)
-    for batch in plan_batches([tuple(p.shape) for p in params], max_batch_bytes, [p.device for p in params]):
+    batches = plan_batches([tuple(p.shape) for p in params], max_batch_bytes, [p.device for p in params])
+
+    def run(batch: list[int]) -> None:
         rows, cols = params[batch[0]].shape
         dev = params[batch[0]].device
         # Row stride padded to 16 bytes so that TMA can address shapes like 40 x 24 too.
@@ -98,8 +116,13 @@ def orthogonalized_updates(
         slot = (rows * ld + 7) // 8 * 8
         gs, ms, ps = [grads[i] for i in batch], [momenta[i] for i in batch], [params[i] for i in batch]
         stack = torch.empty((len(batch), slot), dtype=torch.bfloat16, device=dev)
+        # Large matrices skip the normalisation pass (muon_utils.FOLD_NORMALIZATION_MIN_NUMEL): the momentum kernel
+        # writes the un-normalised bf16 update in its one pass and the iteration divides in its first two epilogues.
+        fold_min = muon_utils.FOLD_NORMALIZATION_MIN_NUMEL
+        defer = bool(schedule) and ld == cols and fold_min > 0 and rows * cols >= fold_min and min(rows, cols) > 128
+        scales = torch.empty((len(batch), 2), dtype=torch.float32, device=dev) if defer else None
         if ld == cols:
-            _native.muon_prepare_batch(gs, ms, ps, momentum, nesterov, l2_weight_decay, eps, stack)
+            _native.muon_prepare_batch(gs, ms, ps, momentum, nesterov, l2_weight_decay, eps, stack, scales)
             X = stack[:, : rows * cols].unflatten(1, (rows, cols))
         else:
             dense = torch.empty((len(batch), (rows * cols + 7) // 8 * 8), dtype=torch.bfloat16, device=dev)
@@ -107,9 +130,30 @@ def orthogonalized_updates(
             X = stack[:, : rows * ld].unflatten(1, (rows, ld))[:, :, :cols]
             X.copy_(dense[:, : rows * cols].unflatten(1, (rows, cols)))
         if schedule:
-            X = _native.newton_schulz_bf16(X, schedule, use_syrk)
+            X = _native.newton_schulz_bf16(X, schedule, use_syrk, scales=scales)
         elif not X.is_contiguous():
             X = X.contiguous()
         for k, i in enumerate(batch):
             out[i] = X[k]
+
+    one_device = len({p.device for p in params}) == 1
+    if NS_STREAMS <= 1 or len(batches) < 2 or not one_device or not params[0].is_cuda:
+        for batch in batches:
+            run(batch)
+        return out  # type: ignore[return-value]
+
+    dev = params[0].device
+    cur = torch.cuda.current_stream(dev)
+    streams = _streams(dev, min(NS_STREAMS, len(batches)))
+    fork = torch.cuda.Event()
+    fork.record(cur)
+    for s in streams:
+        s.wait_event(fork)
+    for k, batch in enumerate(batches):
+        with torch.cuda.stream(streams[k % len(streams)]):
+            run(batch)
+    for s in streams:
+        cur.wait_stream(s)
+    for t in out:
+        t.record_stream(cur)  # allocated on a side stream, consumed on the caller's
     return out  # type: ignore[return-value]

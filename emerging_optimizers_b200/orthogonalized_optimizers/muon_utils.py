@@ -221,6 +221,16 @@ def _apply(
     return out_t.mT
 
 
+# Matrices of at least this many elements (and more than 128 rows on the short side) take the deferred Frobenius
+# normalisation on the bf16 path: one pass writes bf16(x) and the sum of squares, and the division is applied in the
+# epilogues of the first Gram and the first update product.  The first iterate is then bf16(x) / |x| instead of
+# bf16(x / |x|): the same accuracy, different last bits.  On a large matrix that is invisible in the result
+# (1024 x 4096, five "simple" steps: 5.3e-3 from the reference's bf16 result either way); on matrices of a few
+# hundred elements single roundings show (up to 1e-1 on a 16 x 32 case), so those keep the reference's order of
+# operations.  0 disables it.
+FOLD_NORMALIZATION_MIN_NUMEL = 1 << 22
+
+
 # Smallest tensor-parallel group for which S = b A + c A^2 is computed in row blocks, one per rank, and all-gathered,
 # instead of redundantly on every rank as the reference does.  A rank's block costs 2 m^3 / P FLOP as a general
 # product against m^3 for the symmetric kernel on the whole matrix, so the split pays from four ranks on.
@@ -412,10 +422,27 @@ def newton_schulz(
                 ns_step_fn = newton_schulz_step_tsyrk if x.ndim == 2 else batched_newton_schulz_step_tsyrk
         logging.log_first_n(logging.INFO, "Using BF16 I/O kernels for Newton-Schulz iteration.", 1)
 
+    native_fn = _NATIVE_STEP_FNS.get(ns_step_fn)
+
+    if (
+        bf16_path
+        and native_fn is not None
+        and tp_group is None
+        and not normalize_in_double
+        and schedule
+        and FOLD_NORMALIZATION_MIN_NUMEL > 0
+        and x.size(-2) * x.size(-1) >= FOLD_NORMALIZATION_MIN_NUMEL
+        and min(x.size(-2), x.size(-1)) > 128
+    ):
+        # Deferred normalisation: no pass of its own (see FOLD_NORMALIZATION_MIN_NUMEL).
+        x_phys = x.mT if transpose else x  # the input's own orientation
+        natural = transpose == (x_phys.size(-2) > x_phys.size(-1))
+        if natural and x_phys.stride(-1) == 1 and x_phys.size(-1) % 8 == 0 and _native.is_matrix_layout(x_phys):
+            xb, scales = _native.cast_sumsq(x_phys, eps)
+            return _native.newton_schulz_bf16(xb, schedule, native_fn, out_dtype=torch.float32, scales=scales)
+
     # Normalise and (on the bf16 path) narrow in one pass over x.
     X = _normalize(x, eps, tp_group, normalize_in_double, torch.bfloat16 if bf16_path else torch.float32)
-
-    native_fn = _NATIVE_STEP_FNS.get(ns_step_fn)
 
     # Whole loop in one library call when nothing needs to happen between the products: no Gram all-reduce, step
     # functions not replaced, default orientation and (bf16 path, which reads the iterate by TMA) addressable rows.

@@ -177,6 +177,20 @@ int eo_normalize_f32(const float* x, int batch, int64_t rows, int64_t cols, int6
                      void* out, int64_t ldo, int64_t strideo, int out_fp32, int round_bf16, void* stream);
 
 /*
+ * First half of a deferred Frobenius normalisation: ONE pass over the fp32 batch writes it rounded to bf16,
+ * un-normalised (out_bf16, leading dimension ldo, batch stride strideo), and accumulates the sum of squares of the
+ * fp32 values as eo_sumsq_f32 does; scales[2 b] = 1 / max(norm_b, eps)^2 and scales[2 b + 1] = 1 / max(norm_b, eps)
+ * (fp32, on the device) are what eo_newton_schulz_bf16 takes as `dev_scales`.  sumsq may be NULL.  Scratch as for
+ * eo_sumsq_f32.  Saves one of the two reads of the input that "sum of squares, then divide and narrow" needs.
+ *
+ * Stands in for the norm and the division of
+ * emerging_optimizers/orthogonalized_optimizers/muon_utils.py:216 together with the bf16 cast of :262.
+ */
+int eo_cast_sumsq_f32(const float* x, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t stride,
+                      void* out_bf16, int64_t ldo, int64_t strideo, float eps, double* sumsq, float* scales,
+                      void* scratch, size_t scratch_bytes, void* stream);
+
+/*
  * Elementwise parts of one Muon step on a flat, contiguous, 16-byte-aligned fp32 parameter of `numel`
  * elements.  With g' = g + l2_weight_decay * p, lerp(a, b, w) as torch.lerp computes it:
  *
@@ -211,6 +225,10 @@ int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t 
  *       (sumsq[i], device double[n]) and the normalised bf16 tensor written to
  *       out_stack + i * slot_stride - the stacked (n, rows, cols) input of a batched Newton-Schulz run.
  *       `p` may be NULL when l2_weight_decay == 0.  scratch: eo_muon_prepare_scratch_bytes(n, numel).
+ *       With `dev_scales` (device float[2 n]) the normalisation is deferred: out_stack receives bf16(u), not
+ *       divided, in the same single pass that updates the momentum (g and m are read once instead of twice), and
+ *       dev_scales[2 i], dev_scales[2 i + 1] = 1 / max(norm_i, eps)^2, 1 / max(norm_i, eps) are handed to
+ *       eo_newton_schulz_bf16, which applies them in its first two epilogues.  NULL keeps the two-pass form.
  *   eo_muon_apply_batch  : weight update of n tensors of any sizes; update[i] is bf16 or fp32 for all i.
  *       max_blocks_per_tensor > 0 caps the grid (blocks of 256 threads per tensor) so that an update running
  *       beside tensor-core kernels on another stream takes only a slice of the SMs and of HBM bandwidth;
@@ -221,7 +239,8 @@ int eo_muon_apply_f32(float* p, const void* update, int update_is_bf16, int64_t 
 size_t eo_muon_prepare_scratch_bytes(int n, int64_t numel);
 int eo_muon_prepare_batch(int n, const float* const* g, float* const* m, const float* const* p, int64_t numel,
                           double momentum, int nesterov, float l2_weight_decay, float eps, void* out_stack,
-                          int64_t slot_stride, double* sumsq, void* scratch, size_t scratch_bytes, void* stream);
+                          int64_t slot_stride, double* sumsq, float* dev_scales, void* scratch, size_t scratch_bytes,
+                          void* stream);
 int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int update_is_bf16, const int64_t* numel,
                         const float* scale, float shrink, float extra_scale, float lr, int max_blocks_per_tensor,
                         void* stream);
@@ -239,17 +258,22 @@ int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int u
  * `flags`: bit 0 selects the lower-triangular kernel for A and S (falls back to the general kernel when rows
  * or cols is not a multiple of 8); bit 1 disables the fused small-matrix kernel.  That kernel is used for
  * batches of wide matrices with rows <= 128 (per-head / split-QKV blocks, cols >= 256, steps <= 16): one
- * persistent kernel runs every iteration of a matrix with A, A^2 and S kept in shared memory, reading the
- * iterate twice and writing it once per iteration.  `host_abc` is a host array of 3 * steps floats.
+ * persistent kernel runs every iteration of a matrix with A, A^2 and S kept in shared memory; the first
+ * iteration reads the iterate twice, every iteration reads it once (its new value feeds the next Gram matrix
+ * while still in shared memory) and writes it once.  `host_abc` is a host array of 3 * steps floats.
  * `workspace`: eo_newton_schulz_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
+ * `dev_scales`: NULL when X is already normalised.  Otherwise X is the un-normalised bf16 image written by
+ * eo_cast_sumsq_f32 and dev_scales its per-matrix factors: the first Gram epilogue multiplies by 1 / norm^2, the
+ * first update epilogue by 1 / norm, so the Frobenius normalisation costs no pass of its own (not available for
+ * the small-matrix kernel).  The first iterate is then rounded to bf16 before instead of after the division.
  *
  * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 with
  * the step functions of :348-476; launches 3 * steps (2 * steps when c == 0) kernels, or one.
  */
 size_t eo_newton_schulz_workspace_bytes(int batch, int rows, int cols);
 int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, int64_t stride, const float* host_abc,
-                          int steps, int flags, void* out, int out_fp32, int64_t ldo, int64_t strideo,
-                          void* workspace, size_t workspace_bytes, void* stream);
+                          int steps, int flags, void* out, int out_fp32, int64_t ldo, int64_t strideo, void* workspace,
+                          size_t workspace_bytes, const float* dev_scales, void* stream);
 
 /*
  * The same loop for the fp32 ("highest" / "high") path: `steps` iterations on a normalised fp32 iterate X (batch x

@@ -265,3 +265,22 @@ def test_layer_parallel_is_a_torch_optimizer_with_parameter_groups(monkeypatch):
     assert all(p.grad is None for p in b)
     with pytest.raises(ValueError, match="closure is not supported"):
         lp.step(lambda: 0.0)
+
+
+def test_bucket_plan_by_shape_stacks_equal_shapes_and_ends_with_the_smallest():
+    layer = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336)]
+    shapes = layer * 32
+    numels = [a * b for a, b in shapes]
+    world = 8
+    owners = partition_by_cost([ns_cost(s) for s in shapes], world)
+    buckets = _plan_buckets(numels, owners, world, 64 * 1024 * 1024, shapes)
+    seen = sorted(i for b in buckets for r in range(world) for i, _ in b.per_rank[r])
+    assert seen == list(range(len(shapes)))  # every matrix exactly once
+    for b in buckets:
+        for r in range(world):
+            assert len({shapes[i] for i, _ in b.per_rank[r]}) <= 1  # one shape per rank and bucket: one batched run
+    for r in range(world):
+        sizes = [numels[b.per_rank[r][0][0]] for b in buckets if b.per_rank[r]]
+        assert sizes == sorted(sizes, reverse=True)  # largest matrices first, smallest in the last buckets
+        last = [b for b in buckets if b.per_rank[r]][-1]
+        assert all(shapes[i] == (1024, 4096) for i, _ in last.per_rank[r])

@@ -198,3 +198,37 @@ def test_per_head_muon_subclass_pattern():
     want.add_(per_head * scale * 1.0, alpha=-kw["lr"])
     assert torch.equal(p.detach(), want)
     assert nat.read_device_status() == 0
+
+
+def test_fused_step_with_deferred_normalisation_on_large_matrices(monkeypatch):
+    """Matrices of 2^22 elements and more go through the one-pass prepare kernel (momentum update + un-normalised
+    bf16 update + sum of squares) and take their 1 / norm factors in the first two epilogues of the iteration.
+    Momentum buffers are the same bits as with the two-pass form; the weights agree with it within what one bf16
+    rounding of the first iterate moves them, and with the library-GEMM restatement of the step."""
+    shapes = [(1024, 4096), (1024, 4096), (4096, 1024)]
+
+    def make():
+        return [torch.nn.Parameter(randn_tensor(*s, seed=90 + i, scale=0.02, device="cuda")) for i, s in enumerate(shapes)]
+
+    def grads(ps, step):
+        for i, p in enumerate(ps):
+            p.grad = randn_tensor(*p.shape, seed=2000 * (step + 1) + i, scale=1e-3, device="cuda").bfloat16().float()
+
+    a, b = make(), make()
+    p0 = [p.detach().clone() for p in a]
+    deferred, two_pass = Muon(a, use_syrk=True, **KW), Muon(b, use_syrk=True, **KW)
+    for step in range(2):
+        grads(a, step)
+        grads(b, step)
+        deferred.step()
+        monkeypatch.setattr(muon_utils, "FOLD_NORMALIZATION_MIN_NUMEL", 0)
+        two_pass.step()
+        monkeypatch.undo()
+        for pa, pb in zip(a, b):
+            assert torch.equal(deferred.state[pa]["momentum_buffer"], two_pass.state[pb]["momentum_buffer"])
+    for pa, pb, q in zip(a, b, p0):
+        # compare the accumulated updates, not the weights (which are dominated by their initial values)
+        ua, ub = pa.detach() - q * (1 - KW["lr"] * KW["weight_decay"]) ** 2, pb.detach() - q * (1 - KW["lr"] * KW["weight_decay"]) ** 2
+        assert not torch.equal(pa, pb)
+        assert float((ua - ub).norm() / ub.norm()) <= 2e-2
+    assert nat.read_device_status() == 0

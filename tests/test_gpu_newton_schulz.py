@@ -353,3 +353,35 @@ def test_config5_per_head_batch():
     assert float(per_head) <= BF16_TOL
     want = orc.newton_schulz(x[:2].cpu().numpy(), 5, "simple", precision="medium")
     assert rel_fro(y[:2].cpu(), torch.from_numpy(want)) <= BF16_TOL
+
+
+@pytest.mark.parametrize("shape", [(1024, 4096), (4096, 1024), (2, 1024, 4096)])
+def test_deferred_normalisation_is_exact_when_the_norm_is_a_power_of_two(shape, monkeypatch):
+    """Large matrices skip the normalisation pass: bf16(x) is iterated and 1 / |x|^2, 1 / |x| are applied in the first
+    two epilogues.  With entries +-1 and 2^22 of them per matrix the norm is 2^11, every scaling is exact, and the
+    result must equal the normalise-first path bit for bit."""
+    g = torch.Generator(device="cpu").manual_seed(80)
+    x = (torch.randint(0, 2, shape, generator=g).float() * 2 - 1).cuda()
+    for use_syrk in (False, True):
+        with fp32_matmul_precision("medium"):
+            folded = muon_utils.newton_schulz(x, 5, "simple", use_syrk=use_syrk)
+            monkeypatch.setattr(muon_utils, "FOLD_NORMALIZATION_MIN_NUMEL", 0)
+            plain = muon_utils.newton_schulz(x, 5, "simple", use_syrk=use_syrk)
+            monkeypatch.undo()
+        assert torch.equal(folded, plain)
+    assert nat.read_device_status() == 0
+
+
+def test_deferred_normalisation_stays_within_the_bf16_tolerance_on_random_input(monkeypatch):
+    x = randn_tensor(2048, 4096, seed=81)
+    for ctype, steps in (("simple", 5), ("quintic", 5), ("cubic5", 5), ("polar_express", 1)):
+        with fp32_matmul_precision("medium"):
+            folded = muon_utils.newton_schulz(x, steps, ctype, use_syrk=True)
+            monkeypatch.setattr(muon_utils, "FOLD_NORMALIZATION_MIN_NUMEL", 0)
+            plain = muon_utils.newton_schulz(x, steps, ctype, use_syrk=True)
+            monkeypatch.undo()
+        ref = newton_schulz_torch(x, steps, ctype, bf16=True)
+        assert not torch.equal(folded, plain)  # the first iterate is rounded at a different point ...
+        assert rel_fro(folded, ref) <= BF16_TOL and rel_fro(plain, ref) <= BF16_TOL  # ... with the same accuracy
+        assert rel_fro(folded, ref) <= 1.5 * rel_fro(plain, ref) + 1e-3
+    assert nat.read_device_status() == 0
