@@ -429,7 +429,6 @@ def headline_section(ctx: Ctx, args) -> dict:
     ms_total = e0.elapsed_time(e1)
     launches = _native.launch_count - launches0
     timer, _native.launch_timer = (_native.launch_timer or []), None
-    clocks = sampler.stop() if rank == 0 else {}
     if args.kernels_only:
         dense, sym = flops(M, N_COLS, NS_STEPS)
         nb = max(args.batch, 1)
@@ -476,6 +475,7 @@ def headline_section(ctx: Ctx, args) -> dict:
     f1.record()
     ctx.barrier()
     ms_e2e = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else {}  # sampled over both timed regions
     status = _native.read_device_status(dev)
     ms_total, ms_e2e = ctx.max_over_ranks(ms_total, ms_e2e)
     del bufs, peer, gather_buf
