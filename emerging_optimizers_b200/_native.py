@@ -112,6 +112,8 @@ _PROTOTYPES: dict[str, tuple] = {
         + [c_int, c_int, c_int, c_float, c_float, c_void_p],
     ),
     "eo_peek_device_status_async": (c_int, [c_void_p, c_void_p]),
+    "eo_tp_gram_mirror": (c_int, [c_void_p, c_int, c_int64, c_void_p]),
+    "eo_multicast_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "eo_normalize_f32": (
         c_int,
         [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_void_p, c_float, c_int]
@@ -676,6 +678,22 @@ def gemm_multicast(
             M, N, K, alpha, beta, _stream(a),
         )  # fmt: skip
     _check(rc, "eo_gemm_multicast")
+
+
+def tp_gram_mirror(gram: torch.Tensor, n: int, ld: int) -> None:
+    """Copy the lower triangle of the local ``n x n`` bf16 Gram buffer onto its upper triangle."""
+    with torch.cuda.device(gram.device), _Timed("tp_mirror", 1, gram.device):
+        rc = lib().eo_tp_gram_mirror(gram.data_ptr(), n, ld, _stream(gram))
+    _check(rc, "eo_tp_gram_mirror")
+
+
+def multicast_copy(src: torch.Tensor, dst_mc_ptr: int) -> None:
+    """Store the contiguous tensor ``src`` through the multicast address ``dst_mc_ptr`` (see ``eo_multicast_copy``)."""
+    require_cuda(src, "src")
+    assert src.is_contiguous()
+    with torch.cuda.device(src.device), _Timed("multicast_copy", 1, src.device):
+        rc = lib().eo_multicast_copy(src.data_ptr(), dst_mc_ptr, src.numel() * src.element_size(), _stream(src))
+    _check(rc, "eo_multicast_copy")
 
 
 def peek_device_status_async(pinned: torch.Tensor, device: torch.device) -> None:

@@ -63,6 +63,7 @@ DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
+int g_option_tp_lower_only = 1;  // eo_set_option("tp_lower_only"): the exchange fills the lower triangle only
 int g_option_peer_wait_ms = 10000;  // eo_set_option("peer_wait_ms"): budget of one wait for other ranks' flags
 
 int device_setup(DeviceInfo** out) {
@@ -295,6 +296,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     p.tp_partials_mc = static_cast<const unsigned short*>(tp->partials_mc);
     p.tp_gram_mc = static_cast<unsigned short*>(tp->gram_mc);
     p.tp_ld = tp->ld_gram;
+    p.tp_lower_only = g_option_tp_lower_only;
     // cycles at the nominal clock; the SMs never run faster than that, so the wait is at least as long as asked
     p.tp_wait_cycles = static_cast<long long>(g_option_peer_wait_ms) * dev->clock_khz;
     for (int r = 0; r < tp->world; ++r) {
@@ -351,6 +353,11 @@ int eo_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_tile_m") == 0) {
     if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
     g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "tp_lower_only") == 0) {
+    if (value != 0 && value != 1) return fail(EO_ERR_BAD_ARG, "tp_lower_only must be 0 or 1");
+    g_option_tp_lower_only = value;
     return EO_OK;
   }
   if (strcmp(name, "peer_wait_ms") == 0) {
@@ -969,6 +976,34 @@ int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, 
   // into every rank's Gram matrix (both triangles) from the reducer warps of the same CTAs.
   return launch_gemm(X, x_trans, ldx, 0, 0, X, x_trans, ldx, 0, 0, nullptr, 0, 0, nullptr, 0, 0, 1, N, N, K, 1.0f, 0.0f,
                      1.0f, 0, 0, 0, /*tri=*/1, 0, stream, &tp);
+}
+
+int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (gram == nullptr || N <= 0 || ld_gram < N) return fail(EO_ERR_BAD_ARG, "bad Gram matrix");
+  const int nb = (N + 31) / 32;
+  eo::mirror_lower_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned short*>(gram), N, ld_gram);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
+}
+
+int eo_multicast_copy(const void* src, void* dst_multicast, size_t bytes, void* stream) {
+  DeviceInfo* dev = nullptr;
+  if (int rc = device_setup(&dev)) return rc;
+  if (bytes == 0) return EO_OK;
+  if (src == nullptr || dst_multicast == nullptr) return fail(EO_ERR_BAD_ARG, "null pointer");
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst_multicast)) & 15) || bytes % 16 != 0)
+    return fail(EO_ERR_BAD_ARG, "multicast copy needs 16-byte aligned pointers and a size that is a multiple of 16");
+  const long long nvec = static_cast<long long>(bytes / 16);
+  long long blocks = (nvec + 256 * 8 - 1) / (256 * 8);
+  if (blocks > 4LL * dev->sm_count) blocks = 4LL * dev->sm_count;
+  if (blocks < 1) blocks = 1;
+  eo::multicast_copy_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst_multicast), nvec);
+  EO_CUDA(cudaGetLastError());
+  return EO_OK;
 }
 
 size_t eo_sumsq_noalloc_max_partials(void) { return kNoAllocMaxPartials; }

@@ -111,6 +111,7 @@ struct GemmParams {
   unsigned short* tp_gram[8];       // every rank's Gram matrix, N x tp_ld bf16
   long long tp_ld;
   long long tp_wait_cycles;         // budget of one wait for the other ranks' flags
+  int tp_lower_only;                // reducer stores the lower triangle only (the caller mirrors its own copy)
   // D is a multicast address (general product, bf16 D, N a multiple of 32): every store goes to all ranks.
   int d_mc;
   // Deferred Frobenius normalisation: per-matrix factors on the device (two floats per batch entry, see
@@ -668,6 +669,70 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
         gave_up = (*tp_give_up != 0);
       }
       const long long tile_off = static_cast<long long>(sub) * kBlockM * p.bn;
+      if (p.tp_lower_only) {
+        // Lower triangle only: consecutive threads take consecutive 16-byte groups of a tile row, so a warp reads
+        // and stores whole rows (512 contiguous bytes for 256-column tiles); groups above the diagonal are skipped.
+        const int vpr = p.bn / 8;  // groups per tile row
+        const int total = kBlockM * vpr;
+        for (int v0 = rt; v0 < total; v0 += 4 * kTpReducerThreads) {
+          uint4 w[4];
+          bool use[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int v = v0 + i * kTpReducerThreads;
+            const int r = v / vpr, c8 = (v - r * vpr) * 8;
+            const int row = m0 + r, col = n0 + c8;
+            use[i] = v < total && row < p.N && col <= row;
+            if (!use[i]) continue;
+            const long long off = tile_off + static_cast<long long>(r) * p.bn + c8;
+            if (gave_up) {
+              w[i] = make_uint4(kTpPoison, kTpPoison, kTpPoison, kTpPoison);
+            } else if (p.tp_partials_mc != nullptr) {
+              w[i] = multimem_ld_reduce_bf16x8(p.tp_partials_mc + off);
+            } else {
+              float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+              for (int src = 0; src < p.tp_world; ++src) {
+                const uint4 x = ld_relaxed_sys_16(p.tp_partials_peer[src] + off);
+                const unsigned int xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  acc[2 * e] += __uint_as_float(xs[e] << 16);
+                  acc[2 * e + 1] += __uint_as_float(xs[e] & 0xFFFF0000u);
+                }
+              }
+              unsigned int o[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                o[e] = static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * e]))) |
+                       (static_cast<unsigned int>(__bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * e + 1]))) << 16);
+              w[i] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (!use[i]) continue;
+            const int v = v0 + i * kTpReducerThreads;
+            const int r = v / vpr, c8 = (v - r * vpr) * 8;
+            const int row = m0 + r, col = n0 + c8;
+            const long long at = static_cast<long long>(row) * p.tp_ld + col;
+            if (col + 7 <= row) {
+              if (p.tp_gram_mc != nullptr) {
+                multimem_st_16(p.tp_gram_mc + at, w[i]);
+              } else {
+                for (int d = 0; d < p.tp_world; ++d) *reinterpret_cast<uint4*>(p.tp_gram[d] + at) = w[i];
+              }
+            } else {
+              const unsigned int ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+              for (int e = 0; e < 8; ++e) {
+                if (col + e > row) break;
+                const unsigned short h = static_cast<unsigned short>(ws[e >> 1] >> ((e & 1) * 16));
+                for (int d = 0; d < p.tp_world; ++d) p.tp_gram[d][at + e] = h;
+              }
+            }
+          }
+        }
+        continue;
+      }
       for (int cb = 0; cb < nsub; ++cb) {
         const int col0 = n0 + cb * 32;
         if (col0 >= p.N || col0 > m0 + kBlockM - 1) break;  // outside the matrix, or wholly above the diagonal
@@ -773,6 +838,39 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
       p.sched[1] = 0u;
       __threadfence();
     }
+  }
+}
+
+// Copy the strict lower triangle of an N x N bf16 matrix onto its upper triangle (32 x 32 blocks through shared
+// memory, coalesced on both sides).  blockIdx.x enumerates the blocks on and below the diagonal.
+__global__ void __launch_bounds__(256) mirror_lower_kernel(unsigned short* __restrict__ a, int N, long long ld) {
+  __shared__ unsigned short tile[32][33];
+  const int t = blockIdx.x;  // block (bi, bj), bi >= bj, from the linear index t = bi (bi + 1) / 2 + bj
+  int bi = static_cast<int>((sqrtf(8.0f * static_cast<float>(t) + 1.0f) - 1.0f) * 0.5f);
+  while (bi * (bi + 1) / 2 > t) --bi;
+  while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
+  const int bj = t - bi * (bi + 1) / 2;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    const int row = bi * 32 + r, col = bj * 32 + tx;
+    if (row < N && col < N) tile[r][tx] = a[static_cast<long long>(row) * ld + col];
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    // destination element (bj * 32 + r, bi * 32 + tx) takes source (bi * 32 + tx, bj * 32 + r)
+    const int drow = bj * 32 + r, dcol = bi * 32 + tx;
+    if (drow < N && dcol < N && dcol > drow) a[static_cast<long long>(drow) * ld + dcol] = tile[tx][r];
+  }
+}
+
+// Copy `nvec` 16-byte groups from local memory through a multicast address: every rank mapped by `dst_mc` receives
+// them at the same offset.  Consecutive threads store consecutive groups, so a warp emits 512 contiguous bytes.
+__global__ void __launch_bounds__(256) multicast_copy_kernel(const uint4* __restrict__ src, uint4* dst_mc,
+                                                             long long nvec) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const uint4 v = src[i];
+    multimem_st_16(dst_mc + i, v);
   }
 }
 

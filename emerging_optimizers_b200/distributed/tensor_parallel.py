@@ -40,6 +40,15 @@ __all__ = ["GramExchange", "fused_gram_available", "fused_gram", "sharded_gram_p
 # Synchronise and check the device status after every exchange (costs the launch-ahead of the caller's stream).
 STRICT = os.environ.get("EO_TP_STRICT", "0") == "1"
 
+# The exchange delivers the lower triangle only and every rank mirrors its own copy (whole-row accesses in the
+# reducers, half the NVLink bytes); False lets the reducers store the mirror image over NVLink themselves.
+LOWER_ONLY = os.environ.get("EO_TP_LOWER_ONLY", "1") == "1"
+
+# How the row blocks of S = b A + c A^2 reach the other ranks: "copy" (default): plain product into the local
+# buffer, then one multicast copy kernel (512 contiguous bytes per warp); "epilogue": the product's epilogue
+# stores through the multicast address itself (one kernel, but 16-byte multicast stores at a row stride).
+POLY_GATHER = os.environ.get("EO_TP_POLY", "copy")
+
 # process group -> {(m, device index): GramExchange}; entries die with their group
 _EXCHANGES: "weakref.WeakKeyDictionary[dist.ProcessGroup, dict[tuple, GramExchange]]" = weakref.WeakKeyDictionary()
 
@@ -111,11 +120,14 @@ class GramExchange:
         """
         self.raise_if_failed()
         self.seq += 1
+        _native.set_option("tp_lower_only", 1 if LOWER_ONLY else 0)
         _native.tp_gram_allreduce(x, self.world, self.rank, self._partial_ptrs, self._flag_ptrs, self._gram_ptrs,
                                   self._partials_mc, self._gram_mc, self.ld, self.seq)  # fmt: skip
         # Orders every owner's stores before any rank reads its Gram matrix, and every owner's reads of the partial
         # tiles before the next exchange overwrites them.
         self._barrier()
+        if LOWER_ONLY:
+            _native.tp_gram_mirror(self._gram_local, self.m, self.ld)
         _native.peek_device_status_async(self._host_status, self.device)
         if STRICT:
             self.raise_if_failed(synchronize=True)
@@ -130,8 +142,12 @@ class GramExchange:
         rows = m // world
         r0 = self.rank * rows
         S = self.poly.local.view(m, m)
-        _native.gemm_multicast(A[r0 : r0 + rows], A, A[r0 : r0 + rows], S[r0 : r0 + rows],
-                               self.poly.multicast_ptr + r0 * m * 2, alpha=c, beta=b)  # fmt: skip
+        if POLY_GATHER == "epilogue":
+            _native.gemm_multicast(A[r0 : r0 + rows], A, A[r0 : r0 + rows], S[r0 : r0 + rows],
+                                   self.poly.multicast_ptr + r0 * m * 2, alpha=c, beta=b)  # fmt: skip
+        else:
+            _native.gemm(A[r0 : r0 + rows], A, A[r0 : r0 + rows], S[r0 : r0 + rows], alpha=c, beta=b)
+            _native.multicast_copy(S[r0 : r0 + rows], self.poly.multicast_ptr + r0 * m * 2)
         # every rank's rows have landed everywhere; also keeps the next iteration's stores behind this one's readers
         self.poly.barrier()
         return S

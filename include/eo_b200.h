@@ -44,8 +44,8 @@ const char* eo_last_error(void);
  * Tuning knobs (process-wide).  "gemm_tile_m": 0 (default) lets each launch choose between 128-row tiles and
  * 256-row tiles (two MMAs per k-step sharing one B tile: fewer operand bytes per FLOP, used for large problems
  * with long K); 128 or 256 forces one.  Results do not depend on the choice.  "peer_wait_ms" (default 10000):
- * how long a kernel waits for a flag that another rank has to raise before it gives up (see
- * eo_tp_gram_allreduce).
+ * how long a kernel waits for a flag that another rank has to raise before it gives up; "tp_lower_only" (default 1):
+ * see eo_tp_gram_allreduce.
  */
 int eo_set_option(const char* name, int value);
 
@@ -318,7 +318,9 @@ int eo_newton_schulz_f32(const float* X, int batch, int rows, int cols, int64_t 
  * matrices, or both NULL.  `seq` must increase by one with every call on the same buffers (first call: 1).
  * After the call and a barrier across the ranks (which orders the owners' stores before the readers, and every
  * rank's reads of the partial buffers before the next call overwrites them) every rank's Gram matrix holds the
- * full symmetric sum.
+ * full symmetric sum - or, with the option "tp_lower_only" (default 1), its lower triangle, which every rank
+ * completes on its own copy with eo_tp_gram_mirror: the reducers then read and store whole tile rows (512
+ * contiguous bytes per warp) and half as many bytes cross NVLink.
  *
  * Stands in for tsyrk_ex + torch.distributed.all_reduce at
  * emerging_optimizers/orthogonalized_optimizers/muon_utils.py:434-436 (and :370-372).
@@ -329,6 +331,18 @@ int eo_tp_gram_allreduce(const void* X, int x_trans, int64_t ldx, int N, int K, 
                          void* const* partial_ptrs, void* const* flag_ptrs, void* const* gram_ptrs,
                          const void* partials_multicast, void* gram_multicast, int64_t ld_gram, uint32_t seq,
                          void* stream);
+
+/* Copies the strict lower triangle of the N x N bf16 matrix `gram` (leading dimension ld_gram) onto its upper one. */
+int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream);
+
+/*
+ * Copies `bytes` bytes (a multiple of 16, both pointers 16-byte aligned) from local memory through a multicast
+ * (NVLS) address: the data lands at the same offset in the buffer of every rank the address maps.  The
+ * tensor-parallel iteration uses it to all-gather the row blocks of S = b A + c A^2 (each rank copies its block;
+ * 512 contiguous bytes per warp).  The caller orders readers behind a barrier across the ranks.
+ * Stands in for the all-gather a sharded torch.addmm (muon_utils.py:374) needs; no call site in the reference.
+ */
+int eo_multicast_copy(const void* src, void* dst_multicast, size_t bytes, void* stream);
 
 /*
  * General bf16 product D = alpha * op(A) op(B)^T + beta * C (single matrix, conventions of eo_gemm) whose result
