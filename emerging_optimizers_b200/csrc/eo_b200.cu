@@ -673,7 +673,7 @@ namespace {
 // All iterations of a batch of small wide matrices (rows <= 128 <= ... cols) in one persistent kernel.
 int launch_ns_small(DeviceInfo* dev, void* X, int batch, int rows, int cols, int64_t ld, int64_t stride,
                     const float* host_abc, int steps, void* T, int64_t ldt, int64_t t_stride, void* out, int out_fp32,
-                    int64_t ldo, int64_t strideo, void* stream) {
+                    int64_t ldo, int64_t strideo, const float* dev_scales, void* stream) {
   eo::SmallMaps maps;
   memset(&maps, 0, sizeof(maps));
   if (int rc = make_map(&maps.x[0], X, 2, cols, rows, batch, ld, stride, 64, 128)) return rc;
@@ -696,6 +696,7 @@ int launch_ns_small(DeviceInfo* dev, void* X, int batch, int rows, int cols, int
   p.strideo = strideo;
   p.out_fp32 = out_fp32;
   p.status = dev->status_ptr;
+  p.dev_scale = dev_scales;
   {
     std::lock_guard<std::mutex> lock(g_mu);
     p.sched = dev->sched_ptr + 2 * (dev->sched_next % kSchedSlots);
@@ -732,11 +733,9 @@ int eo_newton_schulz_bf16(void* X, int batch, int rows, int cols, int64_t ld, in
 
   // Matrices whose Gram matrix is a single tile take the fused kernel: A, A^2 and S stay in shared memory.
   const bool small = !(flags & 2) && rows <= 128 && rows <= cols && cols >= 256 && steps <= eo::kSmallMaxSteps;
-  if (small && dev_scales != nullptr)
-    return fail(EO_ERR_BAD_ARG, "deferred normalisation (dev_scales) is not available for matrices of up to 128 rows");
   if (small)
     return launch_ns_small(dev, X, batch, rows, cols, ld, stride, host_abc, steps, T, L.ldt, L.t_stride, out, out_fp32,
-                           ldo, strideo, stream);
+                           ldo, strideo, dev_scales, stream);
 
   // Iterate buffers: step i reads `cur` and writes `nxt`; the last step writes `out`.
   void* cur = X;

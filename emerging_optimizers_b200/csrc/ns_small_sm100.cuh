@@ -51,6 +51,9 @@ struct SmallParams {
   int out_fp32;
   unsigned int* sched;   // {next matrix, finished CTAs}
   unsigned int* status;
+  // Deferred Frobenius normalisation: when set, buf[0] holds the un-normalised bf16 input and dev_scale[2 b],
+  // dev_scale[2 b + 1] = 1 / norm_b^2, 1 / norm_b; the first Gram epilogue and the first update epilogue apply them.
+  const float* dev_scale;
 };
 
 struct SmallMaps {
@@ -411,10 +414,13 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
       }
       if (b < 0) break;
       if (p.steps > 0) unit = (unit + nk) % kSmallUnits;  // the Gram pass of the input consumed nk units
+      const float s_gram = (p.dev_scale != nullptr) ? __ldg(p.dev_scale + 2 * b) : 1.0f;
+      const float s_x = (p.dev_scale != nullptr) ? __ldg(p.dev_scale + 2 * b + 1) : 1.0f;
       for (int it = 0; it < p.steps && ok; ++it) {
         const float ca = p.abc[3 * it], cb = p.abc[3 * it + 1], cc = p.abc[3 * it + 2];
         const bool quintic = cc != 0.0f;
         const bool last = (it == p.steps - 1);
+        const bool scaled = (it == 0) && (p.dev_scale != nullptr);  // un-normalised iterate: see SmallParams
         // ---- Gram epilogue: A (bf16) into shared memory, operand layout
         ok = wait_acc_g();
         if (!ok) break;
@@ -426,8 +432,13 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
             unsigned int w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const unsigned int lo = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(acc[8 * q + 2 * e])));
-              const unsigned int hi = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(acc[8 * q + 2 * e + 1])));
+              float g0 = __uint_as_float(acc[8 * q + 2 * e]), g1 = __uint_as_float(acc[8 * q + 2 * e + 1]);
+              if (scaled) {
+                g0 *= s_gram;
+                g1 *= s_gram;
+              }
+              const unsigned int lo = __bfloat16_as_ushort(__float2bfloat16_rn(g0));
+              const unsigned int hi = __bfloat16_as_ushort(__float2bfloat16_rn(g1));
               w[e] = lo | (hi << 16);
             }
             *reinterpret_cast<uint4*>(a_buf + swz_offset(row, c * 32 + q * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -500,6 +511,10 @@ __global__ void __launch_bounds__(kSmallThreads, 1)
                 v[8 * q + 2 * e + 1] =
                     fmaf(ca, __uint_as_float(ws[e] & 0xFFFF0000u), alpha * __uint_as_float(acc[8 * q + 2 * e + 1]));
               }
+            }
+            if (scaled) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] *= s_x;
             }
             if (!last) {
 #pragma unroll

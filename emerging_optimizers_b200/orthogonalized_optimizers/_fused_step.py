@@ -118,8 +118,7 @@ def orthogonalized_updates(
         stack = torch.empty((len(batch), slot), dtype=torch.bfloat16, device=dev)
         # Large matrices skip the normalisation pass (muon_utils.FOLD_NORMALIZATION_MIN_NUMEL): the momentum kernel
         # writes the un-normalised bf16 update in its one pass and the iteration divides in its first two epilogues.
-        fold_min = muon_utils.FOLD_NORMALIZATION_MIN_NUMEL
-        defer = bool(schedule) and ld == cols and fold_min > 0 and rows * cols >= fold_min and min(rows, cols) > 128
+        defer = ld == cols and muon_utils._defer_normalization(rows, cols, len(schedule))
         scales = torch.empty((len(batch), 2), dtype=torch.float32, device=dev) if defer else None
         if ld == cols:
             _native.muon_prepare_batch(gs, ms, ps, momentum, nesterov, l2_weight_decay, eps, stack, scales)

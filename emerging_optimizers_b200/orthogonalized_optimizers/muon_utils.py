@@ -227,8 +227,20 @@ def _apply(
 # bf16(x / |x|): the same accuracy, different last bits.  On a large matrix that is invisible in the result
 # (1024 x 4096, five "simple" steps: 5.3e-3 from the reference's bf16 result either way); on matrices of a few
 # hundred elements single roundings show (up to 1e-1 on a 16 x 32 case), so those keep the reference's order of
-# operations.  0 disables it.
+# operations.  0 disables it.  Stacks of wide matrices of at most 128 rows (the per-head kernel) take it from 2^20
+# elements per matrix: a 128 x 8192 head is as far from the fp32 result either way (1.1e-2 after five "simple" steps).
 FOLD_NORMALIZATION_MIN_NUMEL = 1 << 22
+FOLD_NORMALIZATION_MIN_NUMEL_SMALL = 1 << 20
+
+
+def _defer_normalization(rows: int, cols: int, steps: int) -> bool:
+    """Whether a (stack of) ``rows x cols`` matrices in this physical orientation takes the deferred normalisation."""
+    if FOLD_NORMALIZATION_MIN_NUMEL <= 0 or steps < 1:
+        return False
+    if min(rows, cols) > 128:
+        return rows * cols >= FOLD_NORMALIZATION_MIN_NUMEL
+    small_kernel = rows <= 128 and cols >= 256 and steps <= 16  # what the library routes to the per-head kernel
+    return small_kernel and rows * cols >= FOLD_NORMALIZATION_MIN_NUMEL_SMALL
 
 
 # Smallest tensor-parallel group for which S = b A + c A^2 is computed in row blocks, one per rank, and all-gathered,
@@ -424,20 +436,17 @@ def newton_schulz(
 
     native_fn = _NATIVE_STEP_FNS.get(ns_step_fn)
 
-    if (
-        bf16_path
-        and native_fn is not None
-        and tp_group is None
-        and not normalize_in_double
-        and schedule
-        and FOLD_NORMALIZATION_MIN_NUMEL > 0
-        and x.size(-2) * x.size(-1) >= FOLD_NORMALIZATION_MIN_NUMEL
-        and min(x.size(-2), x.size(-1)) > 128
-    ):
+    if bf16_path and native_fn is not None and tp_group is None and not normalize_in_double and schedule:
         # Deferred normalisation: no pass of its own (see FOLD_NORMALIZATION_MIN_NUMEL).
         x_phys = x.mT if transpose else x  # the input's own orientation
         natural = transpose == (x_phys.size(-2) > x_phys.size(-1))
-        if natural and x_phys.stride(-1) == 1 and x_phys.size(-1) % 8 == 0 and _native.is_matrix_layout(x_phys):
+        if (
+            natural
+            and _defer_normalization(x_phys.size(-2), x_phys.size(-1), len(schedule))
+            and x_phys.stride(-1) == 1
+            and x_phys.size(-1) % 8 == 0
+            and _native.is_matrix_layout(x_phys)
+        ):
             xb, scales = _native.cast_sumsq(x_phys, eps)
             return _native.newton_schulz_bf16(xb, schedule, native_fn, out_dtype=torch.float32, scales=scales)
 

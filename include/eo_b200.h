@@ -264,8 +264,8 @@ int eo_muon_apply_batch(int n, float* const* p, const void* const* update, int u
  * `workspace`: eo_newton_schulz_workspace_bytes(batch, rows, cols) bytes, 256-byte aligned.
  * `dev_scales`: NULL when X is already normalised.  Otherwise X is the un-normalised bf16 image written by
  * eo_cast_sumsq_f32 and dev_scales its per-matrix factors: the first Gram epilogue multiplies by 1 / norm^2, the
- * first update epilogue by 1 / norm, so the Frobenius normalisation costs no pass of its own (not available for
- * the small-matrix kernel).  The first iterate is then rounded to bf16 before instead of after the division.
+ * first update epilogue by 1 / norm (in the small-matrix kernel too), so the Frobenius normalisation costs no
+ * pass of its own.  The first iterate is then rounded to bf16 before instead of after the division.
  *
  * Stands in for the step loop of emerging_optimizers/orthogonalized_optimizers/muon_utils.py:265-269 with
  * the step functions of :348-476; launches 3 * steps (2 * steps when c == 0) kernels, or one.

@@ -385,3 +385,25 @@ def test_deferred_normalisation_stays_within_the_bf16_tolerance_on_random_input(
         assert rel_fro(folded, ref) <= BF16_TOL and rel_fro(plain, ref) <= BF16_TOL  # ... with the same accuracy
         assert rel_fro(folded, ref) <= 1.5 * rel_fro(plain, ref) + 1e-3
     assert nat.read_device_status() == 0
+
+
+def test_deferred_normalisation_in_the_per_head_kernel(monkeypatch):
+    """Stacks of 128 x 8192 heads (2^20 elements each) skip the normalisation pass too: exact with a power-of-two
+    norm, and as close to the library-GEMM restatement as the normalise-first path on random input."""
+    g = torch.Generator(device="cpu").manual_seed(82)
+    ones = (torch.randint(0, 2, (3, 128, 8192), generator=g).float() * 2 - 1).cuda()  # norm 2^10 per head
+    x = randn_tensor(6, 128, 8192, seed=83, scale=1e-3)
+    with fp32_matmul_precision("medium"):
+        folded_ones = muon_utils.newton_schulz(ones, 5, "simple", use_syrk=True)
+        folded = muon_utils.newton_schulz(x, 5, "quintic", use_syrk=True)
+        monkeypatch.setattr(muon_utils, "FOLD_NORMALIZATION_MIN_NUMEL", 0)
+        plain_ones = muon_utils.newton_schulz(ones, 5, "simple", use_syrk=True)
+        plain = muon_utils.newton_schulz(x, 5, "quintic", use_syrk=True)
+        monkeypatch.undo()
+    assert torch.equal(folded_ones, plain_ones)
+    assert not torch.equal(folded, plain)
+    for i in range(x.size(0)):
+        ref = newton_schulz_torch(x[i], 5, "quintic", bf16=True)
+        assert rel_fro(folded[i], ref) <= BF16_TOL and rel_fro(plain[i], ref) <= BF16_TOL
+        assert rel_fro(folded[i], ref) <= 1.5 * rel_fro(plain[i], ref) + 1e-3
+    assert nat.read_device_status() == 0
