@@ -159,7 +159,10 @@ __device__ __forceinline__ float bf16_bits_to_float(unsigned short h) {
 
 // Epilogue for one 32-column chunk held by one thread (row `row`, columns col0..col0+31).
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&acc)[32], long long batch_c,
-                                               long long batch_d, int row, int col0, float alpha, float sum_scale) {
+                                               long long batch_d, int row, int col0, float alpha, float sum_scale,
+                                               const uint4* c_pre = nullptr) {
+  // c_pre: the 64 bytes of bf16 C for this chunk, already loaded by the caller (only given for a full, vector-
+  // addressable chunk; see the prefetch in the epilogue loop).
   if (row >= p.M) return;
   const bool has_c = (p.beta != 0.0f) && (p.C != nullptr);
   const int ncols = min(32, p.N - col0);
@@ -194,7 +197,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       if (full && p.vec_ok) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint4 t = __ldg(reinterpret_cast<const uint4*>(c) + q);
+          const uint4 t = (c_pre != nullptr) ? c_pre[q] : __ldg(reinterpret_cast<const uint4*>(c) + q);
           const unsigned int w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -548,16 +551,34 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
       decode_tile(p, t, b, ti, tj, bm);
       const int m0 = ti * bm + (wide_m ? group * kBlockM : 0);  // first row this set of warps is responsible for
       const int n0 = tj * p.bn;
-      if (!mbar_wait(&acc_full_bar[ab], aphase)) {
-        report(p, kStatusTimeoutEpilogue);
-        break;
-      }
-      tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const int warp_last_row = m0 + quarter * 32 + 31;
       const long long batch_c = static_cast<long long>(b) * p.strideC;
       const long long batch_d = static_cast<long long>(b) * p.strideD;
       const int nchunks = p.bn / 32;
+      // Prefetch of the bf16 C term (the a X of the update, the b A of the Gram polynomial): a chunk's 64 bytes per
+      // thread are requested one chunk ahead - the first chunk's while the tile's last MMAs are still running - so
+      // that their L2 latency is not paid once per chunk inside the epilogue, which the 256-row mode cannot overlap
+      // with the next tile's main loop.  Only full, vector-addressable chunks; the others load inside epilogue_chunk.
+      const bool c_pre_any = !kTp && (p.beta != 0.0f) && (p.C != nullptr) && !p.c_fp32 && p.vec_ok && row < p.M;
+      auto c_pre_ok = [&](int c) {
+        const int col0 = n0 + c * 32;
+        return c_pre_any && c < nchunks && col0 + 32 <= p.N && (!p.tri || row - col0 >= 31);
+      };
+      auto c_pre_load = [&](int c, uint4 (&dst)[4]) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(p.C) + batch_c +
+                                                          static_cast<long long>(row) * p.ldc + n0 + c * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[q] = __ldg(src + q);
+      };
+      uint4 c_cur[4], c_nxt[4];
+      bool have_cur = c_pre_ok(chunk0);
+      if (have_cur) c_pre_load(chunk0, c_cur);
+      if (!mbar_wait(&acc_full_bar[ab], aphase)) {
+        report(p, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
       float alpha = p.alpha, sum_scale = 1.0f;
       if (p.dev_scale != nullptr) {
         if (p.dev_scale_mode == 1)
@@ -613,8 +634,14 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                             static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
                         acc);
+          // the next chunk's C values travel while this chunk is read from TMEM and processed
+          const bool have_nxt = c_pre_ok(c + kChunkStep);
+          if (have_nxt) c_pre_load(c + kChunkStep, c_nxt);
           tmem_ld_wait();
-          epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
+          epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale, have_cur ? c_cur : nullptr);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) c_cur[q] = c_nxt[q];
+          have_cur = have_nxt;
         }
       }
       tc_fence_before();
