@@ -35,7 +35,9 @@ def test_optimizer_steps_match_reference(name, precision):
     for key, val in got.items():
         ref = torch.from_numpy(want[f"{name}.{precision}.{key}"])
         assert val.shape == ref.shape, key
-        if key.endswith("momentum_buffer"):
+        if key.endswith("momentum_buffer") and name != "muown":
+            # plain EMA of the gradients: no kernel of this package is involved.  (Muown's buffer averages the
+            # direction part of the gradient, which depends on the weights the previous steps produced.)
             assert _consumers.rel_fro(val, ref) <= 1e-6, key
         elif ".after" in key and name != "spel":
             w0 = init[int(key[1 : key.index(".")])]

@@ -70,9 +70,10 @@ def test_config1_against_reference(golden_dir):
     x = torch.randn(1024, 4096, generator=g, dtype=torch.float32)
     assert float(x.double().sum()) == pytest.approx(float(rec["x_sum"]), rel=1e-12)
     xg = x.cuda()
-    # The fp32 bound here is 2e-4, not 1e-4: five "simple" steps amplify fp32 round-off on this input so much that
-    # the reference's own fp32 result moves by about 9e-5 when only the BLAS summation order changes.
-    for precision, tol, use_syrk in (("highest", 2e-4, False), ("medium", BF16_TOL, True), ("medium", BF16_TOL, False)):
+    # fp32 bound 1e-4 against the reference's stored CPU fp32 result.  Measured 9.1e-5, nearly all of it the
+    # reference's own distance from a float64 run of the same steps (8.8e-5; the kernels are 1.3e-5 from it, see
+    # tests/test_gpu_reference_edge_cases.py).
+    for precision, tol, use_syrk in (("highest", 1e-4, False), ("medium", BF16_TOL, True), ("medium", BF16_TOL, False)):
         with fp32_matmul_precision(precision):
             y = muon_utils.newton_schulz(xg, 5, "simple", use_syrk=use_syrk)
         err = rel_fro(y[::16, ::16].cpu(), torch.from_numpy(rec[f"{precision}.sample"]))
