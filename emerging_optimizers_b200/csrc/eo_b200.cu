@@ -262,7 +262,19 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
     const int want = g_option_gemm_bm;
     const long long t_wide = (static_cast<long long>((M + 255) / 256) * ((N + 255) / 256)) / (tri ? 2 : 1) * batch;
     const bool fits = precision == 0 && M >= 256 && N >= 256;
-    const bool good = K >= 1024 && 4 * t_wide >= 3LL * dev->sm_count;
+    bool good = K >= 1024 && 4 * t_wide >= 3LL * dev->sm_count;
+    if (good && tp == nullptr) {
+      // Wave quantisation: equal tiles run in rounds of one per SM, so a launch costs ceil(tiles / SMs) tile times.
+      // A 128-row tile takes 0.535 of a 256-row tile's time (half the work at about 7 % less per FLOP); take the
+      // narrow tiles where their rounds come out shorter (e.g. 448 wide tiles = 4 rounds against 896 narrow
+      // tiles = 7 half rounds).
+      const long long sms = dev->sm_count;
+      const long long tm128 = (M + 127) / 128, tn = (N + 255) / 256;
+      const long long t_narrow = (tri ? (tm128 * tn + tn) / 2 : tm128 * tn) * batch;
+      const double cost_wide = static_cast<double>((t_wide + sms - 1) / sms);
+      const double cost_narrow = 0.535 * static_cast<double>((t_narrow + sms - 1) / sms);
+      if (cost_narrow < 0.97 * cost_wide) good = false;
+    }
     if (fits && (want == 256 || (want == 0 && good))) {
       p.bm = 256;
       p.stages = 3;
