@@ -993,9 +993,15 @@ int eo_tp_gram_mirror(void* gram, int N, int64_t ld_gram, void* stream) {
   DeviceInfo* dev = nullptr;
   if (int rc = device_setup(&dev)) return rc;
   if (gram == nullptr || N <= 0 || ld_gram < N) return fail(EO_ERR_BAD_ARG, "bad Gram matrix");
-  const int nb = (N + 31) / 32;
-  eo::mirror_lower_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<unsigned short*>(gram), N, ld_gram);
+  if (N % 64 == 0 && ld_gram % 8 == 0 && (reinterpret_cast<uintptr_t>(gram) & 15) == 0) {
+    const int nb = N / 64;
+    eo::mirror_lower64_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<unsigned short*>(gram), N, ld_gram);
+  } else {
+    const int nb = (N + 31) / 32;
+    eo::mirror_lower_kernel<<<nb * (nb + 1) / 2, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<unsigned short*>(gram), N, ld_gram);
+  }
   EO_CUDA(cudaGetLastError());
   return EO_OK;
 }

@@ -660,7 +660,11 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
     const int tm128 = (p.M + kBlockM - 1) / kBlockM;
     const int nsub = p.bn / 32;  // 32-column blocks of a tile
     bool gave_up = false;
-    for (int slot = blockIdx.x; slot < p.tp_slots; slot += gridDim.x) {
+    // A unit of reducer work is a quarter (32 rows) of an owned tile when only the lower triangle is stored, so
+    // that the tiles of the last wave - whose reduction nothing hides - are spread over four times as many CTAs.
+    const int parts = p.tp_lower_only ? 4 : 1;
+    for (int unit = blockIdx.x; unit < p.tp_slots * parts; unit += gridDim.x) {
+      const int slot = unit / parts, part = unit - slot * parts;
       const int sub = slot * p.tp_world + p.tp_rank;
       if (sub >= p.tp_total) break;
       // tile (ti, tj) on the 128-row grid: column blocks in order, rows from the diagonal down
@@ -700,8 +704,8 @@ __global__ void __launch_bounds__(kGemmThreads + (kTp ? kTpReducerThreads : 0), 
         // Lower triangle only: consecutive threads take consecutive 16-byte groups of a tile row, so a warp reads
         // and stores whole rows (512 contiguous bytes for 256-column tiles); groups above the diagonal are skipped.
         const int vpr = p.bn / 8;  // groups per tile row
-        const int total = kBlockM * vpr;
-        for (int v0 = rt; v0 < total; v0 += 4 * kTpReducerThreads) {
+        const int total = (part + 1) * (kBlockM / 4) * vpr;
+        for (int v0 = part * (kBlockM / 4) * vpr + rt; v0 < total; v0 += 4 * kTpReducerThreads) {
           uint4 w[4];
           bool use[4];
 #pragma unroll
@@ -887,6 +891,44 @@ __global__ void __launch_bounds__(256) mirror_lower_kernel(unsigned short* __res
     // destination element (bj * 32 + r, bi * 32 + tx) takes source (bi * 32 + tx, bj * 32 + r)
     const int drow = bj * 32 + r, dcol = bi * 32 + tx;
     if (drow < N && dcol < N && dcol > drow) a[static_cast<long long>(drow) * ld + dcol] = tile[tx][r];
+  }
+}
+
+// The same for N a multiple of 64 and 16-byte aligned rows: 64 x 64 blocks, 16-byte loads and stores on both sides
+// (eight source rows are gathered from shared memory for every stored group).
+__global__ void __launch_bounds__(256) mirror_lower64_kernel(unsigned short* __restrict__ a, int N, long long ld) {
+  __shared__ unsigned short tile[64][64 + 2];
+  const int t = blockIdx.x;
+  int bi = static_cast<int>((sqrtf(8.0f * static_cast<float>(t) + 1.0f) - 1.0f) * 0.5f);
+  while (bi * (bi + 1) / 2 > t) --bi;
+  while ((bi + 1) * (bi + 2) / 2 <= t) ++bi;
+  const int bj = t - bi * (bi + 1) / 2;
+  for (int v = threadIdx.x; v < 512; v += 256) {  // source block (bi, bj), rows r, groups of eight columns
+    const int r = v >> 3, c8 = (v & 7) * 8;
+    const uint4 w = *reinterpret_cast<const uint4*>(a + static_cast<long long>(bi * 64 + r) * ld + bj * 64 + c8);
+    const unsigned int ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      tile[r][c8 + 2 * e] = static_cast<unsigned short>(ws[e] & 0xFFFFu);
+      tile[r][c8 + 2 * e + 1] = static_cast<unsigned short>(ws[e] >> 16);
+    }
+  }
+  __syncthreads();
+  for (int v = threadIdx.x; v < 512; v += 256) {  // destination block (bj, bi): row bj*64 + r takes source column r
+    const int r = v >> 3, c8 = (v & 7) * 8;
+    const int drow = bj * 64 + r, dcol = bi * 64 + c8;
+    unsigned short* dst = a + static_cast<long long>(drow) * ld + dcol;
+    if (dcol > drow) {  // the whole group lies above the diagonal
+      uint4 w;
+      w.x = tile[c8 + 0][r] | (static_cast<unsigned int>(tile[c8 + 1][r]) << 16);
+      w.y = tile[c8 + 2][r] | (static_cast<unsigned int>(tile[c8 + 3][r]) << 16);
+      w.z = tile[c8 + 4][r] | (static_cast<unsigned int>(tile[c8 + 5][r]) << 16);
+      w.w = tile[c8 + 6][r] | (static_cast<unsigned int>(tile[c8 + 7][r]) << 16);
+      *reinterpret_cast<uint4*>(dst) = w;
+    } else if (dcol + 7 > drow) {  // diagonal block: element by element
+      for (int e = 0; e < 8; ++e)
+        if (dcol + e > drow) dst[e] = tile[c8 + e][r];
+    }
   }
 }
 

@@ -23,7 +23,10 @@ import torch
 import torch.distributed as dist
 
 
-__all__ = ["PeerBuffer"]
+__all__ = ["PeerBuffer", "MULTICAST_PUSH"]
+
+# all_gather_slots pushes a slot with one multicast-store kernel instead of P - 1 copy-engine transfers.
+MULTICAST_PUSH = os.environ.get("EO_MULTICAST_PUSH", "0") == "1"
 
 
 class PeerBuffer:
@@ -71,6 +74,14 @@ class PeerBuffer:
         cur = torch.cuda.current_stream(self.device)
         mine = base + self.rank * slot_numel
         src = self.local[mine : mine + slot_numel]
+        if MULTICAST_PUSH and self.multicast_ptr and (slot_numel * src.element_size()) % 16 == 0:
+            # One kernel reads the slot once and stores it through the NVSwitch multicast address: 1 / (P - 1) of
+            # the local HBM reads and NVLink egress of P - 1 point-to-point copies (the switch replicates).
+            from emerging_optimizers_b200 import _native
+
+            _native.multicast_copy(src, self.multicast_ptr + mine * src.element_size())
+            self.barrier()
+            return
         ready = torch.cuda.Event()
         ready.record(cur)
         for k in range(1, self.world):

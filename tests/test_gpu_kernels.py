@@ -205,3 +205,15 @@ def test_kronecker_factor_update_matches_fp64(shape):
         with pytest.raises(ValueError, match="Kronecker factor must be"):
             update_kronecker_factors([R, L], g, 0.95)
     assert nat.read_device_status() == 0
+
+
+@pytest.mark.parametrize("n", [64, 200, 512, 1000, 4096])
+def test_mirror_of_the_lower_triangle(n):
+    """eo_tp_gram_mirror (both of its kernels: 64 x 64 blocks with vector accesses, 32 x 32 blocks for odd sizes)."""
+    ld = (n + 7) // 8 * 8
+    g = torch.Generator(device="cpu").manual_seed(n)
+    a = torch.randn(n, ld, generator=g).to(torch.bfloat16).cuda()
+    want = torch.tril(a[:, :n]) + torch.tril(a[:, :n], -1).T
+    nat.tp_gram_mirror(a, n, ld)
+    assert torch.equal(a[:, :n], want)
+    assert nat.read_device_status() == 0
