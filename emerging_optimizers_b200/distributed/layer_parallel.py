@@ -135,6 +135,8 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             torch.distributed is not initialised).
         bucket_numel: elements per rank and exchange; smaller buckets start communicating earlier, larger ones
             give the batched Newton-Schulz runs more matrices per launch.  A bucket holds matrices of one shape.
+            The default (32 Mi elements) was the fastest of 16 / 32 / 64 / 256 Mi on the Llama-3-8B-shaped step on
+            eight GPUs (73.6 / 65.1 / 67.6 / 81.5 ms).
         exchange_dtype: dtype of the gathered updates.  ``None`` picks bf16 on the "medium" path (lossless there)
             and fp32 otherwise.
         exchange: "updates": all-gather the orthogonalized updates, every rank applies all of them.
@@ -160,7 +162,7 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         extra_scale_factor: float = 1.0,
         use_syrk: bool = False,
         group: "dist.ProcessGroup | None" = None,
-        bucket_numel: int = 64 * 1024 * 1024,
+        bucket_numel: int = 32 * 1024 * 1024,
         exchange_dtype: torch.dtype | None = None,
         exchange: str = "updates",
     ) -> None:
