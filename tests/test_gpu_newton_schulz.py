@@ -374,6 +374,9 @@ def test_deferred_normalisation_is_exact_when_the_norm_is_a_power_of_two(shape, 
 
 
 def test_deferred_normalisation_stays_within_the_bf16_tolerance_on_random_input(monkeypatch):
+    """Against the library-GEMM restatement (which rounds the first iterate where the normalise-first path does, so
+    that path agrees with it more closely by construction) both stay within the bf16 tolerance; against the fp32
+    path of the same call, which favours neither, the two are equally accurate."""
     x = randn_tensor(2048, 4096, seed=81)
     for ctype, steps in (("simple", 5), ("quintic", 5), ("cubic5", 5), ("polar_express", 1)):
         with fp32_matmul_precision("medium"):
@@ -381,10 +384,12 @@ def test_deferred_normalisation_stays_within_the_bf16_tolerance_on_random_input(
             monkeypatch.setattr(muon_utils, "FOLD_NORMALIZATION_MIN_NUMEL", 0)
             plain = muon_utils.newton_schulz(x, steps, ctype, use_syrk=True)
             monkeypatch.undo()
+        with fp32_matmul_precision("highest"):
+            exact = muon_utils.newton_schulz(x, steps, ctype)
         ref = newton_schulz_torch(x, steps, ctype, bf16=True)
         assert not torch.equal(folded, plain)  # the first iterate is rounded at a different point ...
-        assert rel_fro(folded, ref) <= BF16_TOL and rel_fro(plain, ref) <= BF16_TOL  # ... with the same accuracy
-        assert rel_fro(folded, ref) <= 1.5 * rel_fro(plain, ref) + 1e-3
+        assert rel_fro(folded, ref) <= BF16_TOL and rel_fro(plain, ref) <= BF16_TOL
+        assert rel_fro(folded, exact) <= 1.25 * rel_fro(plain, exact) + 5e-4  # ... with the same accuracy
     assert nat.read_device_status() == 0
 
 
@@ -406,5 +411,4 @@ def test_deferred_normalisation_in_the_per_head_kernel(monkeypatch):
     for i in range(x.size(0)):
         ref = newton_schulz_torch(x[i], 5, "quintic", bf16=True)
         assert rel_fro(folded[i], ref) <= BF16_TOL and rel_fro(plain[i], ref) <= BF16_TOL
-        assert rel_fro(folded[i], ref) <= 1.5 * rel_fro(plain[i], ref) + 1e-3
     assert nat.read_device_status() == 0
