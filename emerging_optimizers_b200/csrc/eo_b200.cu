@@ -14,6 +14,7 @@
 
 #include "elementwise.cuh"
 #include "gemm_sm100.cuh"
+#include "gemm_pair_sm100.cuh"
 #include "ns_small_sm100.cuh"
 
 namespace {
@@ -63,6 +64,7 @@ DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
+int g_option_gemm_pair = 0;  // eo_set_option("gemm_pair"): 256-row tiles on CTA pairs (tcgen05 cta_group::2)
 int g_option_tp_lower_only = 1;  // eo_set_option("tp_lower_only"): the exchange fills the lower triangle only
 int g_option_peer_wait_ms = 10000;  // eo_set_option("peer_wait_ms"): budget of one wait for other ranks' flags
 
@@ -90,6 +92,8 @@ int device_setup(DeviceInfo** out) {
                                  eo::kGemmTpSmemBytes));
     EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kGemmTpSmemBytes));
+    EO_CUDA(cudaFuncSetAttribute(eo::eo_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 eo::kPairSmemBytes));
     d.clock_khz = prop.clockRate;
     EO_CUDA(cudaFuncSetAttribute(eo::eo_ns_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  eo::kSmallSmemBytes));
@@ -337,7 +341,11 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   }
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (tp != nullptr) {
+  if (g_option_gemm_pair && tp == nullptr && !d_multicast && precision == 0 && p.bm == 256 && p.bn == 256) {
+    // CTA pairs: one cluster of two CTAs per tile in flight
+    const int pairs = p.total_tiles < dev->sm_count / 2 ? p.total_tiles : dev->sm_count / 2;
+    eo::eo_gemm_pair_kernel<<<2 * pairs, eo::kGemmThreads, eo::kPairSmemBytes, st>>>(maps, p);
+  } else if (tp != nullptr) {
     constexpr int threads = eo::kGemmThreads + eo::kTpReducerThreads;
     if (p.bm == 256)
       eo::eo_gemm_kernel<2, true><<<grid, threads, eo::kGemmTpSmemBytes, st>>>(maps, p);
@@ -365,6 +373,11 @@ int eo_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_tile_m") == 0) {
     if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
     g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "gemm_pair") == 0) {
+    if (value != 0 && value != 1) return fail(EO_ERR_BAD_ARG, "gemm_pair must be 0 or 1");
+    g_option_gemm_pair = value;
     return EO_OK;
   }
   if (strcmp(name, "tp_lower_only") == 0) {

@@ -1,0 +1,307 @@
+// The GEMM / SYRK of gemm_sm100.cuh on CTA pairs: tcgen05.mma with cta_group::2.
+//
+// Two CTAs of one TPC (a cluster of two) share every 256 x 256 output tile.  CTA r of the pair holds rows
+// 128 r .. 128 r + 127 of the tile: it loads those rows of A and rows 128 r .. of the tile's B operand (its half of
+// N) into its own shared memory, and the accumulator for its rows lives in its own TMEM.  One thread of the leader
+// CTA (rank 0) issues the MMAs for both: M = 256 across the pair, the B halves are read from both CTAs' shared
+// memory by the hardware.  Compared with the 256-row mode of the single-CTA kernel this keeps its operand traffic per
+// FLOP (32 KiB per CTA, k-step and 128 x 256 x 64 block) but needs only 256 TMEM columns per tile, so two
+// accumulators alternate and the epilogue of tile t overlaps the main loop of tile t + 1, and each SM reads only
+// half of B from its shared memory; stages are 32 KiB, so the ring is six deep.
+//
+// Cross-CTA protocol (all barriers live at the same offsets in both CTAs; "L:" = the leader's copy is used):
+//   full[s]      L: operand stage s loaded.  The leader's producer expects 64 KiB; both CTAs' TMA loads count their
+//                   bytes on the leader's barrier (cta_group::2 loads, no multicast).
+//   empty[s]        stage s free again; the leader's MMA thread commits to its own and to the peer's barrier.
+//   acc_full[a]     accumulator a complete; committed to both CTAs likewise.
+//   acc_empty[a] L: accumulator a drained; the epilogue warps of both CTAs arrive (the peer's remotely).
+//   tq_full[q]      tile index q published; the leader's producer takes tiles from the global counter, writes the
+//                   index into both CTAs' queues and arrives on both barriers.
+//   tq_empty[q]  L: queue slot q consumed by every role of both CTAs.
+// Every wait is bounded; a wait that runs out records a code in the status word and the role leaves its loop.
+#pragma once
+
+#include "gemm_sm100.cuh"
+
+namespace eo {
+
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = 2 * kStageABytes;  // A half (128 x 64 bf16) + B half (128 x 64 bf16)
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 512 + 1024;
+constexpr uint32_t kStatusPair = 0x60u;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    eo_gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
+  uint64_t* full_bar = bars;                           // [kPairStages]
+  uint64_t* empty_bar = full_bar + kPairStages;        // [kPairStages]
+  uint64_t* acc_full_bar = empty_bar + kPairStages;    // [2]
+  uint64_t* acc_empty_bar = acc_full_bar + 2;          // [2]
+  uint64_t* tq_full_bar = acc_empty_bar + 2;           // [kTileQueue]
+  uint64_t* tq_empty_bar = tq_full_bar + kTileQueue;   // [kTileQueue]
+  int* tile_queue = reinterpret_cast<int*>(tq_empty_bar + kTileQueue);  // [kTileQueue]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tile_queue + kTileQueue);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: leader (issues the MMAs, owns the shared barriers), 1: peer
+  const bool leader = rank == 0;
+  const uint32_t peer = rank ^ 1u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full_bar[s], 1);
+      mbar_init(&acc_empty_bar[s], 2 * kEpilogueWarps);  // the epilogue warps of both CTAs
+    }
+    for (int s = 0; s < kTileQueue; ++s) {
+      mbar_init(&tq_full_bar[s], 1);
+      // leader: MMA thread + epilogue warps; peer: producer + epilogue warps
+      mbar_init(&tq_empty_bar[s], 2 * (1 + kEpilogueWarps));
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&maps.a[0]);
+    tma_prefetch_desc(&maps.b[0]);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised and TMEM is allocated before anything crosses over
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr int bk = kBlockK;
+  constexpr int bm = 2 * kBlockM;  // pair tile height
+  const int num_kb = (p.K + bk - 1) / bk;
+  const uint32_t leader_mask = kPairLeaderMask;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int tq = 0;
+      uint32_t tq_phase = 0;
+      bool ok = true;
+      while (ok) {
+        int t;
+        if (leader) {
+          t = static_cast<int>(atomicAdd(p.sched, 1u));
+          if (t >= p.total_tiles) t = -1;
+          if (!mbar_wait_cluster(&tq_empty_bar[tq], tq_phase ^ 1u)) {
+            report(p, kStatusPair + 1u);
+            break;
+          }
+          tile_queue[tq] = t;
+          st_cluster_u32(mapa_u32(smem_u32(&tile_queue[tq]), peer), static_cast<uint32_t>(t));
+          mbar_arrive(&tq_full_bar[tq]);
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tq_full_bar[tq]), peer));
+        } else {
+          if (!mbar_wait_cluster(&tq_full_bar[tq], tq_phase)) {
+            report(p, kStatusPair + 2u);
+            break;
+          }
+          t = tile_queue[tq];
+          mbar_arrive_cluster(smem_u32(&tq_empty_bar[tq]) & leader_mask);
+        }
+        if (++tq == kTileQueue) {
+          tq = 0;
+          tq_phase ^= 1u;
+        }
+        if (t < 0) break;
+        int b, ti, tj;
+        decode_tile(p, t, b, ti, tj, bm);
+        const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;   // this CTA's rows of A
+        const int n0 = tj * p.bn + static_cast<int>(rank) * kBlockM;  // this CTA's half of B (rows of op(B))
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u)) {
+            report(p, kStatusPair + 3u);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kPairStageBytes;
+          uint8_t* sb = sa + kStageABytes;
+          const uint32_t fb = smem_u32(&full_bar[stage]) & leader_mask;
+          if (leader) mbar_expect_tx(&full_bar[stage], 2u * kPairStageBytes);  // both CTAs' bytes
+          const int k0 = kb * bk;
+          if (!p.a_mn) {
+            tma_load_3d_pair(sa, &maps.a[0], fb, k0, m0, b);  // box {bk, 128, 1}
+          } else {
+            for (int q = 0; q < kBlockM / bk; ++q)  // box {bk (M), bk (K), 1}
+              tma_load_3d_pair(sa + q * bk * kRowBytes, &maps.a[0], fb, m0 + q * bk, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d_pair(sb, &maps.b[0], fb, k0, n0, b);
+          } else {
+            for (int q = 0; q < kBlockM / bk; ++q)
+              tma_load_3d_pair(sb + q * bk * kRowBytes, &maps.b[0], fb, n0 + q * bk, k0, b);
+          }
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && elect_one()) {
+      const uint32_t idesc = make_idesc(1u, p.a_mn != 0, p.b_mn != 0, bm, p.bn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int ab = 0;
+      uint32_t aphase = 0;
+      int tq = 0;
+      uint32_t tq_phase = 0;
+      bool ok = true;
+      while (ok) {
+        if (!mbar_wait(&tq_full_bar[tq], tq_phase)) {
+          report(p, kStatusPair + 4u);
+          break;
+        }
+        const int t = tile_queue[tq];
+        mbar_arrive(&tq_empty_bar[tq]);
+        if (++tq == kTileQueue) {
+          tq = 0;
+          tq_phase ^= 1u;
+        }
+        if (t < 0) break;
+        if (!mbar_wait_cluster(&acc_empty_bar[ab], aphase ^ 1u)) {
+          report(p, kStatusPair + 5u);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_cluster(&full_bar[stage], phase)) {
+            report(p, kStatusPair + 6u);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+          const uint32_t sb = sa + static_cast<uint32_t>(kStageABytes);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * p.adv_a, p.lbo_a, p.sbo_a);
+            const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
+            umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(smem_u32(&empty_bar[stage]));
+          umma_commit_pair(mapa_u32(smem_u32(&empty_bar[stage]), peer));
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(smem_u32(&acc_full_bar[ab]));
+        umma_commit_pair(mapa_u32(smem_u32(&acc_full_bar[ab]), peer));
+        if (++ab == 2) {
+          ab = 0;
+          aphase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    const int quarter = warp & 3;
+    const int group = (warp - 2) >> 2;
+    constexpr int kChunkStep = kEpilogueWarps / 4;
+    int ab = 0;
+    uint32_t aphase = 0;
+    int tq = 0;
+    uint32_t tq_phase = 0;
+    while (true) {
+      if (!mbar_wait_cluster(&tq_full_bar[tq], tq_phase)) {
+        report(p, kStatusPair + 7u);
+        break;
+      }
+      const int t = tile_queue[tq];
+      __syncwarp();
+      if (lane == 0) {
+        if (leader)
+          mbar_arrive(&tq_empty_bar[tq]);
+        else
+          mbar_arrive_cluster(smem_u32(&tq_empty_bar[tq]) & leader_mask);
+      }
+      if (++tq == kTileQueue) {
+        tq = 0;
+        tq_phase ^= 1u;
+      }
+      if (t < 0) break;
+      int b, ti, tj;
+      decode_tile(p, t, b, ti, tj, bm);
+      const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;
+      const int n0 = tj * p.bn;
+      const int row = m0 + quarter * 32 + lane;
+      const int warp_last_row = m0 + quarter * 32 + 31;
+      const long long batch_c = static_cast<long long>(b) * p.strideC;
+      const long long batch_d = static_cast<long long>(b) * p.strideD;
+      const int nchunks = p.bn / 32;
+      float alpha = p.alpha, sum_scale = 1.0f;
+      if (p.dev_scale != nullptr) {
+        if (p.dev_scale_mode == 1)
+          alpha *= __ldg(p.dev_scale + 2 * b);
+        else
+          sum_scale = __ldg(p.dev_scale + 2 * b + 1);
+      }
+      if (!mbar_wait_cluster(&acc_full_bar[ab], aphase)) {
+        report(p, kStatusPair + 8u);
+        break;
+      }
+      tc_fence_after();
+      for (int c = group; c < nchunks; c += kChunkStep) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        if (p.tri && col0 > warp_last_row) break;
+        uint32_t acc[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                          static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
+                      acc);
+        tmem_ld_wait();
+        epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader)
+          mbar_arrive(&acc_empty_bar[ab]);
+        else
+          mbar_arrive_cluster(smem_u32(&acc_empty_bar[ab]) & leader_mask);
+      }
+      if (++ab == 2) {
+        ab = 0;
+        aphase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nothing of this CTA is addressed by its partner any more
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+      p.sched[0] = 0u;
+      p.sched[1] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace eo
