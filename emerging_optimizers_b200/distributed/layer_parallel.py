@@ -44,6 +44,9 @@ from emerging_optimizers_b200.orthogonalized_optimizers.muon import _NS_FUNCTION
 
 __all__ = ["ns_cost", "partition_by_cost", "LayerParallelMuon"]
 
+# exchange="parameters": close every bucket's pushes with a group barrier of its own (only for comparison runs).
+PER_BUCKET_BARRIER = False
+
 
 def ns_cost(shape: Sequence[int]) -> float:
     """Tensor-core FLOPs of one Newton-Schulz iteration on a matrix of this shape (symmetric outputs once)."""
@@ -452,7 +455,11 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
                 ready.record()
             with torch.cuda.stream(side):
                 side.wait_event(ready)
-                peer.all_gather_slots(base, b.slot_numel)
+                # No barrier per bucket: the buckets' regions are disjoint and nobody reads a pushed matrix before
+                # the step ends, so a rank's pushes never wait for the slowest rank's previous bucket.
+                peer.all_gather_slots(base, b.slot_numel, barrier=PER_BUCKET_BARRIER)
+        with torch.cuda.stream(side):
+            peer.barrier()  # every rank's pushes have landed everywhere
         self._join_compute_streams(dev)
         torch.cuda.current_stream().wait_stream(side)
 

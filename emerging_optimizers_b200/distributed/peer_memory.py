@@ -64,12 +64,13 @@ class PeerBuffer:
         """Group barrier enqueued on the current stream (every rank's stream passes it together)."""
         self.handle.barrier(channel=0)
 
-    def all_gather_slots(self, base: int, slot_numel: int) -> None:
+    def all_gather_slots(self, base: int, slot_numel: int, barrier: bool = True) -> None:
         """All-gather in place: region ``base + r * slot_numel`` holds rank r's slot on every rank afterwards.
 
         The caller has filled its own slot of its own buffer.  Enqueued on the current stream: the slot is pushed
         to every peer by copy engines (parallel streams), then the group barrier orders the arrival of all pushes
-        before anything enqueued after this call.
+        before anything enqueued after this call.  With ``barrier=False`` only the pushes are enqueued (a caller that
+        gathers several disjoint regions needs one barrier behind the last of them, not one each).
         """
         cur = torch.cuda.current_stream(self.device)
         mine = base + self.rank * slot_numel
@@ -80,7 +81,8 @@ class PeerBuffer:
             from emerging_optimizers_b200 import _native
 
             _native.multicast_copy(src, self.multicast_ptr + mine * src.element_size())
-            self.barrier()
+            if barrier:
+                self.barrier()
             return
         ready = torch.cuda.Event()
         ready.record(cur)
@@ -91,4 +93,5 @@ class PeerBuffer:
                 s.wait_event(ready)
                 self.peer_view(peer, slot_numel, mine).copy_(src, non_blocking=True)
             cur.wait_stream(s)
-        self.barrier()
+        if barrier:
+            self.barrier()
