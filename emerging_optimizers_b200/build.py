@@ -53,10 +53,14 @@ def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | N
     cmd = [_nvcc(), *NVCC_FLAGS, *(extra_flags or [])]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", OUT, *[os.path.join(CSRC, s) for s in SOURCES]]
+    tmp = f"{OUT}.{os.getpid()}.tmp"  # a reader never sees a half-written library
+    cmd += ["-o", tmp, *[os.path.join(CSRC, s) for s in SOURCES]]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError(f"nvcc failed:\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, OUT)
     if verbose:
         print(res.stderr, file=sys.stderr)
     return OUT

@@ -81,7 +81,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   constexpr int bk = kBlockK;
   constexpr int bm = 2 * kBlockM;  // pair tile height
   const int num_kb = (p.K + bk - 1) / bk;
-  const uint32_t leader_mask = kPairLeaderMask;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
@@ -110,7 +109,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             break;
           }
           t = tile_queue[tq];
-          mbar_arrive_cluster(smem_u32(&tq_empty_bar[tq]) & leader_mask);
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tq_empty_bar[tq]), 0u));
         }
         if (++tq == kTileQueue) {
           tq = 0;
@@ -129,7 +128,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           }
           uint8_t* sa = smem + stage * kPairStageBytes;
           uint8_t* sb = sa + kStageABytes;
-          const uint32_t fb = smem_u32(&full_bar[stage]) & leader_mask;
+          const uint32_t fb = mapa_u32(smem_u32(&full_bar[stage]), 0u);  // the leader's barrier
           if (leader) mbar_expect_tx(&full_bar[stage], 2u * kPairStageBytes);  // both CTAs' bytes
           const int k0 = kb * bk;
           if (!p.a_mn) {
@@ -232,7 +231,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (leader)
           mbar_arrive(&tq_empty_bar[tq]);
         else
-          mbar_arrive_cluster(smem_u32(&tq_empty_bar[tq]) & leader_mask);
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tq_empty_bar[tq]), 0u));
       }
       if (++tq == kTileQueue) {
         tq = 0;
@@ -278,7 +277,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (leader)
           mbar_arrive(&acc_empty_bar[ab]);
         else
-          mbar_arrive_cluster(smem_u32(&acc_empty_bar[ab]) & leader_mask);
+          mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty_bar[ab]), 0u));
       }
       if (++ab == 2) {
         ab = 0;

@@ -213,8 +213,6 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // 128 rows of the accumulator in its own TMEM and half of the B operand in its own shared memory).  No load with
 // cluster multicast is used anywhere: each CTA loads its own operand halves.
 // ---------------------------------------------------------------------------------------------
-constexpr uint32_t kPairLeaderMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address of a pair
-
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -258,8 +256,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   }
   return true;
 }
-// TMA load whose completion bytes are counted on the LEADER CTA's barrier (`leader_bar` = address with the rank bit
-// cleared); the data lands in the executing CTA's own shared memory.  No multicast.
+// TMA load whose completion bytes are counted on the LEADER CTA's barrier (`leader_bar` = its shared::cluster
+// address, from mapa); the data lands in the executing CTA's own shared memory.  No multicast.
 __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int c0,
                                                  int c1, int c2) {
   asm volatile(
