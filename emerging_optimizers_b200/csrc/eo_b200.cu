@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 #include "elementwise.cuh"
@@ -64,9 +65,49 @@ DeviceInfo g_dev[kMaxDevices];
 std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
-int g_option_gemm_pair = 0;  // eo_set_option("gemm_pair"): 256-row tiles on CTA pairs (tcgen05 cta_group::2)
+int g_option_gemm_pair = 1;     // eo_set_option("gemm_pair"): 256-row tiles run on CTA pairs (tcgen05 cta_group::2)
+int g_option_gemm_split_k = 1;  // eo_set_option("gemm_split_k"): the pair kernel may split the K range of its last tiles
 int g_option_tp_lower_only = 1;  // eo_set_option("tp_lower_only"): the exchange fills the lower triangle only
 int g_option_peer_wait_ms = 10000;  // eo_set_option("peer_wait_ms"): budget of one wait for other ranks' flags
+
+// Workspace of the pair kernel's split tail: partial accumulators and arrival counters, one set per device and
+// stream (launches on one stream never overlap), grown on demand and kept until the process exits.
+struct SplitWorkspace {
+  float* ws = nullptr;
+  unsigned int* cnt = nullptr;
+  size_t ws_bytes = 0;
+  size_t cnt_words = 0;
+};
+std::map<std::pair<int, cudaStream_t>, SplitWorkspace> g_split_ws;
+constexpr size_t kSplitWorkspaceLimit = size_t(4) << 30;
+
+int split_workspace(cudaStream_t st, size_t ws_bytes, size_t cnt_words, SplitWorkspace* out) {
+  int dev = 0;
+  EO_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_mu);
+  SplitWorkspace& w = g_split_ws[std::make_pair(dev, st)];
+  if (w.ws_bytes < ws_bytes || w.cnt_words < cnt_words) {
+    if (ws_bytes > kSplitWorkspaceLimit)
+      return fail(EO_ERR_BAD_ARG, "batch too large for the split-K workspace (%zu bytes); launch it in parts",
+                  ws_bytes);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    EO_CUDA(cudaStreamIsCapturing(st, &cap));
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(EO_ERR_UNSUPPORTED, "the split-K workspace of this stream has to grow, which cannot happen during "
+                                      "stream capture; run the same call once on this stream before capturing");
+    // cudaFree waits for the device, so no kernel still uses the old buffers
+    if (w.ws != nullptr) EO_CUDA(cudaFree(w.ws));
+    if (w.cnt != nullptr) EO_CUDA(cudaFree(w.cnt));
+    w = SplitWorkspace();
+    EO_CUDA(cudaMalloc(reinterpret_cast<void**>(&w.ws), ws_bytes));
+    w.ws_bytes = ws_bytes;
+    EO_CUDA(cudaMalloc(reinterpret_cast<void**>(&w.cnt), cnt_words * sizeof(unsigned int)));
+    w.cnt_words = cnt_words;
+    EO_CUDA(cudaMemsetAsync(w.cnt, 0, cnt_words * sizeof(unsigned int), st));
+  }
+  *out = w;
+  return EO_OK;
+}
 
 int device_setup(DeviceInfo** out) {
   int dev = 0;
@@ -262,7 +303,37 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   // pay off when every SM still gets several tiles and K is long enough to hide the un-overlapped epilogue.
   p.bm = 128;
   p.stages = eo::kStages;
-  {
+  // Split tail of the pair kernel: decided from M, N, K and the triangular flag alone (never from the batch size),
+  // so that a batched launch and per-matrix launches of the same shape round identically.  It applies when a
+  // matrix has at least one and a half rounds of 256 x 256 tiles and its last round is so empty that the K range
+  // of those tiles can be cut into two or more pieces that still fit one round.
+  const int pairs_max = dev->sm_count / 2;
+  const bool pair_ok = g_option_gemm_pair && tp == nullptr && !d_multicast && precision == 0 && M >= 256 &&
+                       N >= 256 && pairs_max >= 1 && g_option_gemm_bm != 128;
+  int split_s = 1, split_rest = 0;
+  if (pair_ok && g_option_gemm_split_k && K >= 1024) {
+    const int tm = (M + 255) / 256, tn = (N + 255) / 256;
+    long long tiles1 = 0;
+    if (tri) {
+      for (int j = 0; j < tn; ++j) tiles1 += tm > j ? tm - j : 0;
+    } else {
+      tiles1 = static_cast<long long>(tm) * tn;
+    }
+    const int rest = static_cast<int>(tiles1 % pairs_max);
+    if (2 * tiles1 >= 3LL * pairs_max && rest > 0) {
+      int s = pairs_max / rest;
+      if (s > 8) s = 8;
+      if (s > ((K + bk - 1) / bk) / 8) s = ((K + bk - 1) / bk) / 8;
+      if (s >= 2) {
+        split_s = s;
+        split_rest = rest;
+      }
+    }
+  }
+  if (split_s > 1) {
+    p.bm = 256;
+    p.stages = 3;
+  } else {
     const int want = g_option_gemm_bm;
     const long long t_wide = (static_cast<long long>((M + 255) / 256) * ((N + 255) / 256)) / (tri ? 2 : 1) * batch;
     const bool fits = precision == 0 && M >= 256 && N >= 256;
@@ -341,9 +412,24 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   }
   const int grid = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (g_option_gemm_pair && tp == nullptr && !d_multicast && precision == 0 && p.bm == 256 && p.bn == 256) {
-    // CTA pairs: one cluster of two CTAs per tile in flight
-    const int pairs = p.total_tiles < dev->sm_count / 2 ? p.total_tiles : dev->sm_count / 2;
+  if (pair_ok && p.bm == 256 && p.bn == 256) {
+    // CTA pairs: one cluster of two CTAs per work item in flight
+    p.split_first = p.tiles_per_batch - split_rest;
+    p.split_s = split_s;
+    p.split_items_per_batch = p.split_first + split_rest * split_s;
+    const long long items = static_cast<long long>(p.split_items_per_batch) * batch;
+    if (items > 0x3fffffffLL) return fail(EO_ERR_BAD_ARG, "too many tiles");
+    p.total_tiles = static_cast<int>(items);
+    if (split_rest > 0) {
+      const size_t split_tiles = static_cast<size_t>(split_rest) * batch;
+      SplitWorkspace w;
+      if (int rc = split_workspace(st, split_tiles * split_s * 2 * eo::kSplitHalfFloats * sizeof(float),
+                                   split_tiles * 2 * eo::kEpilogueWarps, &w))
+        return rc;
+      p.split_ws = w.ws;
+      p.split_cnt = w.cnt;
+    }
+    const int pairs = p.total_tiles < pairs_max ? p.total_tiles : pairs_max;
     eo::eo_gemm_pair_kernel<<<2 * pairs, eo::kGemmThreads, eo::kPairSmemBytes, st>>>(maps, p);
   } else if (tp != nullptr) {
     constexpr int threads = eo::kGemmThreads + eo::kTpReducerThreads;
@@ -373,6 +459,11 @@ int eo_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_tile_m") == 0) {
     if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
     g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "gemm_split_k") == 0) {
+    if (value != 0 && value != 1) return fail(EO_ERR_BAD_ARG, "gemm_split_k must be 0 or 1");
+    g_option_gemm_split_k = value;
     return EO_OK;
   }
   if (strcmp(name, "gemm_pair") == 0) {

@@ -19,6 +19,15 @@
 //                   index into both CTAs' queues and arrives on both barriers.
 //   tq_empty[q]  L: queue slot q consumed by every role of both CTAs.
 // Every wait is bounded; a wait that runs out records a code in the status word and the role leaves its loop.
+//
+// Split tail.  Equal tiles run in rounds of one per pair, and the last round of a launch is usually far from full
+// (528 SYRK tiles of an 8192-row Gram matrix on 74 pairs: 7.14 rounds of work take 8).  The launcher can therefore
+// cut the K range of the last `tiles mod pairs` tiles of every matrix into `split_s` pieces, which are scheduled as
+// work items of their own.  A piece writes its fp32 accumulator to a workspace; per epilogue warp a counter is
+// raised, and the warp that raises it last adds the pieces up in piece order (so the result does not depend on who
+// finishes last) and runs the normal epilogue.  Nothing waits for anything.  Which tiles are split depends only on
+// M, N, K and the triangular flag, never on the batch size, so a batched launch and per-matrix launches agree bit
+// for bit.
 #pragma once
 
 #include "gemm_sm100.cuh"
@@ -29,6 +38,39 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kStageABytes;  // A half (128 x 64 bf16) + B half (128 x 64 bf16)
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 512 + 1024;
 constexpr uint32_t kStatusPair = 0x60u;
+constexpr int kPairDiagBit = 1 << 30;
+constexpr int kSplitHalfFloats = kBlockM * kMaxBlockN;  // one CTA's half of one piece's accumulator (128 KiB)
+
+// One unit of work: a whole tile, or one K piece of a tile of the split tail.
+struct PairWork {
+  int tile;   // tile index as decode_tile() numbers them (all matrices of the batch)
+  int kb0;    // first k-block
+  int kb1;    // one past the last k-block
+  int slot;   // index of the split tile among all split tiles of the launch, or -1 for a whole tile
+  int piece;  // which piece of the split tile
+};
+
+__device__ __forceinline__ PairWork decode_pair_work(const GemmParams& p, int w, int num_kb) {
+  PairWork k;
+  const int b = w / p.split_items_per_batch;
+  const int r = w - b * p.split_items_per_batch;
+  if (r < p.split_first) {
+    k.tile = b * p.tiles_per_batch + r;
+    k.kb0 = 0;
+    k.kb1 = num_kb;
+    k.slot = -1;
+    k.piece = 0;
+  } else {
+    const int q = r - p.split_first;
+    const int rt = q / p.split_s;
+    k.piece = q - rt * p.split_s;
+    k.tile = b * p.tiles_per_batch + p.split_first + rt;
+    k.kb0 = static_cast<int>(static_cast<long long>(k.piece) * num_kb / p.split_s);
+    k.kb1 = static_cast<int>(static_cast<long long>(k.piece + 1) * num_kb / p.split_s);
+    k.slot = b * (p.tiles_per_batch - p.split_first) + rt;
+  }
+  return k;
+}
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     eo_gemm_pair_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
@@ -95,12 +137,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (leader) {
           t = static_cast<int>(atomicAdd(p.sched, 1u));
           if (t >= p.total_tiles) t = -1;
+          int entry = t;  // bit 30: the tile lies on the diagonal of a SYRK and A is read from the B operand
+          if (t >= 0 && p.same_ab) {
+            int b, ti, tj;
+            decode_tile(p, decode_pair_work(p, t, num_kb).tile, b, ti, tj, bm);
+            if (ti * bm == tj * p.bn) entry |= kPairDiagBit;
+          }
           if (!mbar_wait_cluster(&tq_empty_bar[tq], tq_phase ^ 1u)) {
             report(p, kStatusPair + 1u);
             break;
           }
-          tile_queue[tq] = t;
-          st_cluster_u32(mapa_u32(smem_u32(&tile_queue[tq]), peer), static_cast<uint32_t>(t));
+          tile_queue[tq] = entry;
+          st_cluster_u32(mapa_u32(smem_u32(&tile_queue[tq]), peer), static_cast<uint32_t>(entry));
           mbar_arrive(&tq_full_bar[tq]);
           mbar_arrive_cluster(mapa_u32(smem_u32(&tq_full_bar[tq]), peer));
         } else {
@@ -109,6 +157,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             break;
           }
           t = tile_queue[tq];
+          if (t >= 0) t &= ~kPairDiagBit;
           mbar_arrive_cluster(mapa_u32(smem_u32(&tq_empty_bar[tq]), 0u));
         }
         if (++tq == kTileQueue) {
@@ -116,11 +165,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           tq_phase ^= 1u;
         }
         if (t < 0) break;
+        const PairWork wk = decode_pair_work(p, t, num_kb);
         int b, ti, tj;
-        decode_tile(p, t, b, ti, tj, bm);
+        decode_tile(p, wk.tile, b, ti, tj, bm);
         const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;   // this CTA's rows of A
         const int n0 = tj * p.bn + static_cast<int>(rank) * kBlockM;  // this CTA's half of B (rows of op(B))
-        for (int kb = 0; kb < num_kb; ++kb) {
+        // SYRK tile on the diagonal: this CTA's rows of A are its rows of the B operand; load them once.
+        const bool a_in_b = p.same_ab && m0 == n0;
+        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
           if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1u)) {
             report(p, kStatusPair + 3u);
             ok = false;
@@ -129,9 +181,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           uint8_t* sa = smem + stage * kPairStageBytes;
           uint8_t* sb = sa + kStageABytes;
           const uint32_t fb = mapa_u32(smem_u32(&full_bar[stage]), 0u);  // the leader's barrier
-          if (leader) mbar_expect_tx(&full_bar[stage], 2u * kPairStageBytes);  // both CTAs' bytes
+          if (leader)  // both CTAs' bytes
+            mbar_expect_tx(&full_bar[stage], a_in_b ? 2u * kStageABytes : 2u * kPairStageBytes);
           const int k0 = kb * bk;
-          if (!p.a_mn) {
+          if (a_in_b) {
+            // nothing to load for A
+          } else if (!p.a_mn) {
             tma_load_3d_pair(sa, &maps.a[0], fb, k0, m0, b);  // box {bk, 128, 1}
           } else {
             for (int q = 0; q < kBlockM / bk; ++q)  // box {bk (M), bk (K), 1}
@@ -166,33 +221,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           report(p, kStatusPair + 4u);
           break;
         }
-        const int t = tile_queue[tq];
+        const int entry = tile_queue[tq];
         mbar_arrive(&tq_empty_bar[tq]);
         if (++tq == kTileQueue) {
           tq = 0;
           tq_phase ^= 1u;
         }
-        if (t < 0) break;
+        if (entry < 0) break;
+        const bool a_in_b = (entry & kPairDiagBit) != 0;
+        const PairWork wk = decode_pair_work(p, entry & ~kPairDiagBit, num_kb);
         if (!mbar_wait_cluster(&acc_empty_bar[ab], aphase ^ 1u)) {
           report(p, kStatusPair + 5u);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(ab * kMaxBlockN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
           if (!mbar_wait_cluster(&full_bar[stage], phase)) {
             report(p, kStatusPair + 6u);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
-          const uint32_t sb = sa + static_cast<uint32_t>(kStageABytes);
+          const uint32_t sb = smem_u32(smem + stage * kPairStageBytes) + static_cast<uint32_t>(kStageABytes);
+          const uint32_t sa = a_in_b ? sb : sb - static_cast<uint32_t>(kStageABytes);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint64_t da = make_smem_desc(sa + k * p.adv_a, p.lbo_a, p.sbo_a);
             const uint64_t db = make_smem_desc(sb + k * p.adv_b, p.lbo_b, p.sbo_b);
-            umma_f16_pair(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16_pair(tmem_d, da, db, idesc, ((kb - wk.kb0) | k) != 0 ? 1u : 0u);
           }
           // the stage is free in both CTAs once these MMAs have read it
           umma_commit_pair(smem_u32(&empty_bar[stage]));
@@ -225,7 +282,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         report(p, kStatusPair + 7u);
         break;
       }
-      const int t = tile_queue[tq];
+      int t = tile_queue[tq];
+      if (t >= 0) t &= ~kPairDiagBit;
       __syncwarp();
       if (lane == 0) {
         if (leader)
@@ -238,8 +296,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         tq_phase ^= 1u;
       }
       if (t < 0) break;
+      const PairWork wk = decode_pair_work(p, t, num_kb);
       int b, ti, tj;
-      decode_tile(p, t, b, ti, tj, bm);
+      decode_tile(p, wk.tile, b, ti, tj, bm);
       const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;
       const int n0 = tj * p.bn;
       const int row = m0 + quarter * 32 + lane;
@@ -259,6 +318,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         break;
       }
       tc_fence_after();
+      // a piece's accumulator goes to the workspace as it is: [chunk][row of this CTA's half][32 columns] fp32
+      float* const ws_tile =
+          wk.slot < 0 ? nullptr
+                      : p.split_ws + (static_cast<size_t>(wk.slot) * p.split_s * 2 + rank) * kSplitHalfFloats +
+                            static_cast<size_t>(quarter * 32 + lane) * 32;
+      constexpr size_t kPieceStride = 2 * static_cast<size_t>(kSplitHalfFloats);
       for (int c = group; c < nchunks; c += kChunkStep) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;
@@ -269,7 +334,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                           static_cast<uint32_t>(ab * kMaxBlockN + c * 32),
                       acc);
         tmem_ld_wait();
-        epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
+        if (wk.slot < 0) {
+          epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
+        } else {
+          float4* dst = reinterpret_cast<float4*>(ws_tile + wk.piece * kPieceStride + static_cast<size_t>(c) * kBlockM * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            __stcg(dst + j, make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]),
+                                        __uint_as_float(acc[4 * j + 2]), __uint_as_float(acc[4 * j + 3])));
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -278,6 +351,46 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           mbar_arrive(&acc_empty_bar[ab]);
         else
           mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty_bar[ab]), 0u));
+      }
+      if (wk.slot >= 0) {
+        // The warp whose arrival completes the count owns the sum: pieces are added in piece order, whoever is last.
+        __threadfence();
+        __syncwarp();
+        unsigned int* cnt = p.split_cnt + (static_cast<size_t>(wk.slot) * 2 + rank) * kEpilogueWarps + (warp - 2);
+        unsigned int old = 0;
+        if (lane == 0) old = atomicAdd(cnt, 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == static_cast<unsigned int>(p.split_s - 1)) {
+          __threadfence();
+          for (int c = group; c < nchunks; c += kChunkStep) {
+            const int col0 = n0 + c * 32;
+            if (col0 >= p.N) break;
+            if (p.tri && col0 > warp_last_row) break;
+            uint32_t acc[32];
+            const float* src = ws_tile + static_cast<size_t>(c) * kBlockM * 32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(src) + j);
+              acc[4 * j] = __float_as_uint(v.x);
+              acc[4 * j + 1] = __float_as_uint(v.y);
+              acc[4 * j + 2] = __float_as_uint(v.z);
+              acc[4 * j + 3] = __float_as_uint(v.w);
+            }
+            for (int piece = 1; piece < p.split_s; ++piece) {
+              const float4* sp = reinterpret_cast<const float4*>(src + piece * kPieceStride);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 v = __ldcg(sp + j);
+                acc[4 * j] = __float_as_uint(__uint_as_float(acc[4 * j]) + v.x);
+                acc[4 * j + 1] = __float_as_uint(__uint_as_float(acc[4 * j + 1]) + v.y);
+                acc[4 * j + 2] = __float_as_uint(__uint_as_float(acc[4 * j + 2]) + v.z);
+                acc[4 * j + 3] = __float_as_uint(__uint_as_float(acc[4 * j + 3]) + v.w);
+              }
+            }
+            epilogue_chunk(p, acc, batch_c, batch_d, row, col0, alpha, sum_scale);
+          }
+          if (lane == 0) *cnt = 0u;  // ready for the next launch on this stream
+        }
       }
       if (++ab == 2) {
         ab = 0;

@@ -119,6 +119,13 @@ struct GemmParams {
   // mode 2 multiplies alpha * acc + beta * C by dev_scale[2 b + 1] before the result is rounded.
   const float* dev_scale;
   int dev_scale_mode;
+  // Split tail of the pair kernel (gemm_pair_sm100.cuh): of every matrix's tiles, those from split_first on are cut
+  // into split_s pieces along K.  split_first == tiles_per_batch: nothing is split.
+  int split_first;
+  int split_s;
+  int split_items_per_batch;  // work items per matrix: split_first + (tiles_per_batch - split_first) * split_s
+  float* split_ws;            // [split tile][piece][CTA of the pair][128 x 256] fp32 partial accumulators
+  unsigned int* split_cnt;    // [split tile][CTA of the pair][epilogue warp] arrivals, zero between launches
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,

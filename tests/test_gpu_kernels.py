@@ -217,3 +217,54 @@ def test_mirror_of_the_lower_triangle(n):
     nat.tp_gram_mirror(a, n, ld)
     assert torch.equal(a[:, :n], want)
     assert nat.read_device_status() == 0
+
+
+@pytest.mark.parametrize(
+    "m,n,k,tri,a_mn,b_mn",
+    [
+        (3072, 3328, 1024, False, 0, 0),  # 156 tiles on 74 CTA pairs: the last 8 are cut in two
+        (3072, 3328, 4160, False, 0, 1),  # ... in eight, K not a multiple of the piece length
+        (3000, 3300, 2048, False, 1, 1),  # ragged edges
+        (4352, 4352, 1536, True, 0, 0),  # SYRK: 153 lower-triangle tiles, the last 5 in three pieces
+    ],
+)
+def test_split_tail_of_the_pair_kernel(m, n, k, tri, a_mn, b_mn):
+    """Large products run on CTA pairs and split the K range of the tiles of their last, nearly empty round.
+
+    Exact on integer-valued inputs; on random inputs equal to the unsplit kernel up to the rounding of the partial
+    sums, the same bits for a batched launch as for per-matrix launches, and the same bits from run to run.
+    """
+    if tri:
+        a = int_tensor(m, k, seed=21)
+        c = int_tensor(m, m, seed=22)
+        c = (c + c.T).contiguous()
+        assert torch.equal(tk.tsyrk_ex(a, c, alpha=0.5, beta=0.25), _exact_ref(a, c, 0.5, 0.25))
+        x = (randn_tensor(2, m, k, seed=23) / 8).bfloat16()
+        run = lambda t: tk.batched_tsyrk_ex(t) if t.dim() == 3 else tk.tsyrk_ex(t)  # noqa: E731
+    else:
+        a = int_tensor(m, k, seed=21) if not a_mn else int_tensor(k, m, seed=21).mT
+        b = int_tensor(k, n, seed=22) if b_mn else int_tensor(n, k, seed=22).mT
+        c = int_tensor(m, n, seed=23)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        nat.gemm(a, b, c, out, alpha=0.5, beta=0.25)
+        assert torch.equal(out, (0.5 * (a.float() @ b.float()) + 0.25 * c.float()).bfloat16())
+        x = (randn_tensor(2, m, k, seed=24) / 8).bfloat16()
+        y = (randn_tensor(2, k, n, seed=25) / 8).bfloat16()
+
+        def run(t):
+            yy = y if t.dim() == 3 else y[0]
+            o = torch.empty(*t.shape[:-1], n, dtype=torch.bfloat16, device="cuda")
+            return nat.gemm(t, yy, None, o)
+
+    both = run(x)
+    one = run(x[0].contiguous())
+    assert torch.equal(both[0], one)  # the split does not depend on the batch size
+    assert torch.equal(run(x), both)  # nor on which CTA finishes a tile
+    nat.set_option("gemm_split_k", 0)
+    try:
+        unsplit = run(x[0].contiguous())
+    finally:
+        nat.set_option("gemm_split_k", 1)
+    assert rel_fro(one.float(), unsplit.float()) <= 2e-3  # both are bf16 roundings of nearly the same fp32 sums
+    if k >= 1536:
+        assert not torch.equal(one, unsplit)  # the split really happened: some roundings differ
