@@ -95,7 +95,10 @@ int split_workspace(cudaStream_t st, size_t ws_bytes, size_t cnt_words, SplitWor
     if (cap != cudaStreamCaptureStatusNone)
       return fail(EO_ERR_UNSUPPORTED, "the split-K workspace of this stream has to grow, which cannot happen during "
                                       "stream capture; run the same call once on this stream before capturing");
-    // cudaFree waits for the device, so no kernel still uses the old buffers
+    // Never shrink either buffer (products of different shapes alternate on a stream).  cudaFree waits for the
+    // device, so no kernel still uses the old buffers.
+    if (ws_bytes < w.ws_bytes) ws_bytes = w.ws_bytes;
+    if (cnt_words < w.cnt_words) cnt_words = w.cnt_words;
     if (w.ws != nullptr) EO_CUDA(cudaFree(w.ws));
     if (w.cnt != nullptr) EO_CUDA(cudaFree(w.cnt));
     w = SplitWorkspace();

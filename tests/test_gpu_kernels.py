@@ -224,7 +224,7 @@ def test_mirror_of_the_lower_triangle(n):
     [
         (3072, 3328, 1024, False, 0, 0),  # 156 tiles on 74 CTA pairs: the last 8 are cut in two
         (3072, 3328, 4160, False, 0, 1),  # ... in eight, K not a multiple of the piece length
-        (3000, 3300, 2048, False, 1, 1),  # ragged edges
+        (3000, 3304, 2048, False, 1, 1),  # ragged edges
         (4352, 4352, 1536, True, 0, 0),  # SYRK: 153 lower-triangle tiles, the last 5 in three pieces
     ],
 )
