@@ -66,6 +66,10 @@ std::mutex g_mu;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 int g_option_gemm_bm = 0;  // eo_set_option("gemm_tile_m"): 0 = choose per problem, 128 or 256 = force
 int g_option_gemm_pair = 1;     // eo_set_option("gemm_pair"): 256-row tiles run on CTA pairs (tcgen05 cta_group::2)
+int g_option_pair_group_m = 16;  // eo_set_option("gemm_pair_group_m" / "gemm_pair_band" / "gemm_pair_hint_a" / "..._b")
+int g_option_pair_band = 0;
+int g_option_pair_hint_a = 0;
+int g_option_pair_hint_b = 0;
 int g_option_gemm_split_k = 1;  // eo_set_option("gemm_split_k"): the pair kernel may split the K range of its last tiles
 int g_option_tp_lower_only = 1;  // eo_set_option("tp_lower_only"): the exchange fills the lower triangle only
 int g_option_peer_wait_ms = 10000;  // eo_set_option("peer_wait_ms"): budget of one wait for other ranks' flags
@@ -417,6 +421,10 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (pair_ok && p.bm == 256 && p.bn == 256) {
     // CTA pairs: one cluster of two CTAs per work item in flight
+    p.pair_group_m = g_option_pair_group_m;
+    p.pair_band = (tri && M == N && p.tiles_m == p.tiles_n) ? g_option_pair_band : 0;
+    p.pair_hint_a = tri ? 0 : g_option_pair_hint_a;
+    p.pair_hint_b = tri ? 0 : g_option_pair_hint_b;
     p.split_first = p.tiles_per_batch - split_rest;
     p.split_s = split_s;
     p.split_items_per_batch = p.split_first + split_rest * split_s;
@@ -462,6 +470,21 @@ int eo_set_option(const char* name, int value) {
   if (strcmp(name, "gemm_tile_m") == 0) {
     if (value != 0 && value != 128 && value != 256) return fail(EO_ERR_BAD_ARG, "gemm_tile_m must be 0, 128 or 256");
     g_option_gemm_bm = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "gemm_pair_group_m") == 0) {
+    if (value < 1 || value > 64) return fail(EO_ERR_BAD_ARG, "gemm_pair_group_m must be 1..64");
+    g_option_pair_group_m = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "gemm_pair_band") == 0) {
+    if (value < 0 || value > 64) return fail(EO_ERR_BAD_ARG, "gemm_pair_band must be 0..64");
+    g_option_pair_band = value;
+    return EO_OK;
+  }
+  if (strcmp(name, "gemm_pair_hint_a") == 0 || strcmp(name, "gemm_pair_hint_b") == 0) {
+    if (value < 0 || value > 2) return fail(EO_ERR_BAD_ARG, "%s must be 0, 1 or 2", name);
+    (name[15] == 'a' ? g_option_pair_hint_a : g_option_pair_hint_b) = value;
     return EO_OK;
   }
   if (strcmp(name, "gemm_split_k") == 0) {

@@ -50,6 +50,51 @@ struct PairWork {
   int piece;  // which piece of the split tile
 };
 
+// Tile order of the pair kernel (256 x 256 tiles).  The tiles in flight at one time (one per pair, 74 on a B200)
+// should touch as few row blocks of the operands as possible: they stream through K together, so an operand block
+// shared by several of them comes from DRAM once.  General products: groups of pair_group_m row blocks, column by
+// column inside a group.  Triangular products: bands of pair_band tile columns, row by row inside a band, so that
+// 74 consecutive tiles form a block of about 9 x 8 tiles instead of two whole tile columns.
+__device__ __forceinline__ void decode_pair_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
+  b = t / p.tiles_per_batch;
+  int r = t - b * p.tiles_per_batch;
+  if (p.tri && p.pair_band > 0) {
+    const int g = p.pair_band, T = p.tiles_m;
+    ti = tj = 0;
+    for (int c0 = 0; c0 < T; c0 += g) {
+      const int rows = T - c0;
+      const int w = rows < g ? rows : g;
+      const int tri_cnt = w * (w + 1) / 2;
+      const int cnt = tri_cnt + (rows - w) * w;
+      if (r < cnt) {
+        if (r < tri_cnt) {
+          int a = 0;
+          while ((a + 1) * (a + 2) / 2 <= r) ++a;
+          ti = c0 + a;
+          tj = c0 + r - a * (a + 1) / 2;
+        } else {
+          const int r2 = r - tri_cnt;
+          ti = c0 + w + r2 / w;
+          tj = c0 + r2 % w;
+        }
+        return;
+      }
+      r -= cnt;
+    }
+  } else if (p.tri) {
+    decode_tile(p, t, b, ti, tj, 2 * kBlockM);
+  } else {
+    const int gm = p.pair_group_m;
+    const int per_group = gm * p.tiles_n;
+    const int g = r / per_group;
+    const int first = g * gm;
+    const int rows = min(gm, p.tiles_m - first);
+    const int w = r - g * per_group;
+    ti = first + (w % rows);
+    tj = w / rows;
+  }
+}
+
 __device__ __forceinline__ PairWork decode_pair_work(const GemmParams& p, int w, int num_kb) {
   PairWork k;
   const int b = w / p.split_items_per_batch;
@@ -132,6 +177,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       int tq = 0;
       uint32_t tq_phase = 0;
       bool ok = true;
+      const uint64_t pol_a = l2_policy(p.pair_hint_a), pol_b = l2_policy(p.pair_hint_b);
+      auto load = [](void* dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int hint, uint64_t pol) {
+        if (hint != 0)
+          tma_load_3d_pair_hint(dst, map, bar, c0, c1, c2, pol);
+        else
+          tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+      };
       while (ok) {
         int t;
         if (leader) {
@@ -140,7 +192,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           int entry = t;  // bit 30: the tile lies on the diagonal of a SYRK and A is read from the B operand
           if (t >= 0 && p.same_ab) {
             int b, ti, tj;
-            decode_tile(p, decode_pair_work(p, t, num_kb).tile, b, ti, tj, bm);
+            decode_pair_tile(p, decode_pair_work(p, t, num_kb).tile, b, ti, tj);
             if (ti * bm == tj * p.bn) entry |= kPairDiagBit;
           }
           if (!mbar_wait_cluster(&tq_empty_bar[tq], tq_phase ^ 1u)) {
@@ -167,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (t < 0) break;
         const PairWork wk = decode_pair_work(p, t, num_kb);
         int b, ti, tj;
-        decode_tile(p, wk.tile, b, ti, tj, bm);
+        decode_pair_tile(p, wk.tile, b, ti, tj);
         const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;   // this CTA's rows of A
         const int n0 = tj * p.bn + static_cast<int>(rank) * kBlockM;  // this CTA's half of B (rows of op(B))
         // SYRK tile on the diagonal: this CTA's rows of A are its rows of the B operand; load them once.
@@ -187,16 +239,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           if (a_in_b) {
             // nothing to load for A
           } else if (!p.a_mn) {
-            tma_load_3d_pair(sa, &maps.a[0], fb, k0, m0, b);  // box {bk, 128, 1}
+            load(sa, &maps.a[0], fb, k0, m0, b, p.pair_hint_a, pol_a);  // box {bk, 128, 1}
           } else {
             for (int q = 0; q < kBlockM / bk; ++q)  // box {bk (M), bk (K), 1}
-              tma_load_3d_pair(sa + q * bk * kRowBytes, &maps.a[0], fb, m0 + q * bk, k0, b);
+              load(sa + q * bk * kRowBytes, &maps.a[0], fb, m0 + q * bk, k0, b, p.pair_hint_a, pol_a);
           }
           if (!p.b_mn) {
-            tma_load_3d_pair(sb, &maps.b[0], fb, k0, n0, b);
+            load(sb, &maps.b[0], fb, k0, n0, b, p.pair_hint_b, pol_b);
           } else {
             for (int q = 0; q < kBlockM / bk; ++q)
-              tma_load_3d_pair(sb + q * bk * kRowBytes, &maps.b[0], fb, n0 + q * bk, k0, b);
+              load(sb + q * bk * kRowBytes, &maps.b[0], fb, n0 + q * bk, k0, b, p.pair_hint_b, pol_b);
           }
           if (++stage == kPairStages) {
             stage = 0;
@@ -298,7 +350,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       if (t < 0) break;
       const PairWork wk = decode_pair_work(p, t, num_kb);
       int b, ti, tj;
-      decode_tile(p, wk.tile, b, ti, tj, bm);
+      decode_pair_tile(p, wk.tile, b, ti, tj);
       const int m0 = ti * bm + static_cast<int>(rank) * kBlockM;
       const int n0 = tj * p.bn;
       const int row = m0 + quarter * 32 + lane;

@@ -126,6 +126,11 @@ struct GemmParams {
   int split_items_per_batch;  // work items per matrix: split_first + (tiles_per_batch - split_first) * split_s
   float* split_ws;            // [split tile][piece][CTA of the pair][128 x 256] fp32 partial accumulators
   unsigned int* split_cnt;    // [split tile][CTA of the pair][epilogue warp] arrivals, zero between launches
+  // Tile order and L2 policies of the pair kernel.
+  int pair_group_m;  // general products: row-block group height (tiles of a group run column by column)
+  int pair_band;     // triangular products: column-band width in tiles (0: column-major through the triangle)
+  int pair_hint_a;   // L2 eviction policy of the A / B operand loads: 0 none, 1 evict first, 2 evict last
+  int pair_hint_b;
 };
 
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
