@@ -885,7 +885,16 @@ def main() -> None:
                     help="muon_step: what the layer-parallel optimizer all-gathers")
     ap.add_argument("--bucket-numel", type=int, default=0,
                     help="muon_step: elements per rank and exchange bucket (0: the optimizer's default)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="set a tuning knob of the native library before running (eo_set_option), e.g. gemm_pair=0; "
+                    "for A/B runs and profiler captures")
     args = ap.parse_args()
+    if args.option and args.impl != "reference":
+        from emerging_optimizers_b200 import _native
+
+        for item in args.option:
+            name, _, value = item.partition("=")
+            _native.set_option(name, int(value))
     if args.shape is not None:
         global M, N_COLS
         M, N_COLS = args.shape

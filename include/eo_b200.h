@@ -43,9 +43,17 @@ const char* eo_last_error(void);
 /*
  * Tuning knobs (process-wide).  "gemm_tile_m": 0 (default) lets each launch choose between 128-row tiles and
  * 256-row tiles (two MMAs per k-step sharing one B tile: fewer operand bytes per FLOP, used for large problems
- * with long K); 128 or 256 forces one.  Results do not depend on the choice.  "peer_wait_ms" (default 10000):
- * how long a kernel waits for a flag that another rank has to raise before it gives up; "tp_lower_only" (default 1):
- * see eo_tp_gram_allreduce.
+ * with long K); 128 or 256 forces one.  Results do not depend on the choice.  "gemm_pair" (default 1): plain bf16
+ * products with 256 x 256 tiles run on CTA pairs (tcgen05 cta_group::2); same bits as with 0.  "gemm_split_k"
+ * (default 1): the pair kernel may cut the K range of the tiles of a launch's last, nearly empty round into pieces
+ * whose fp32 partial sums are added in a fixed order; which tiles are cut depends on M, N, K and the triangular
+ * flag only (never on the batch size), results are deterministic and differ from "gemm_split_k" 0 by the rounding
+ * of those partial sums.  The partial sums live in a per-stream workspace that the library allocates on first use
+ * and keeps; a call that would have to grow it during stream capture fails with EO_ERR_UNSUPPORTED.
+ * "gemm_pair_group_m" (default 8), "gemm_pair_band" (default 8), "gemm_pair_hint_a", "gemm_pair_hint_b" (default
+ * 0): tile order and L2 eviction policies of the pair kernel; results do not depend on them.  "peer_wait_ms"
+ * (default 10000): how long a kernel waits for a flag that another rank has to raise before it gives up;
+ * "tp_lower_only" (default 1): see eo_tp_gram_allreduce.
  */
 int eo_set_option(const char* name, int value);
 
