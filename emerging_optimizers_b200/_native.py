@@ -215,6 +215,36 @@ def read_device_status(device: torch.device | None = None) -> int:
     return int(code.value)
 
 
+# Late but loud: every Newton-Schulz call leaves an asynchronous copy of the status word in pinned host memory and
+# looks at the copy its predecessors left.  A kernel whose bounded wait ran out (its output is then incomplete) thus
+# makes one of the next calls on that GPU raise, without any synchronisation on the way.
+_STATUS_MIRRORS: dict[int, torch.Tensor] = {}
+
+
+def raise_on_earlier_failure(device: torch.device) -> None:
+    """Raise ``NativeLibraryError`` if a kernel of an earlier call on ``device`` gave up a bounded wait."""
+    mirror = _STATUS_MIRRORS.get(device.index if device.index is not None else torch.cuda.current_device())
+    if mirror is None:
+        return
+    code = int(mirror[0])
+    if code != 0:
+        mirror.zero_()
+        read_device_status(device)  # synchronises and clears the device word
+        raise NativeLibraryError(
+            f"a kernel of an earlier call on {device} gave up a bounded wait (device status {code:#x}); "
+            "results computed since then are incomplete"
+        )
+
+
+def note_status(device: torch.device) -> None:
+    """Enqueue the asynchronous copy that a later :func:`raise_on_earlier_failure` looks at."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    mirror = _STATUS_MIRRORS.get(index)
+    if mirror is None:
+        mirror = _STATUS_MIRRORS[index] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    peek_device_status_async(mirror, device)
+
+
 def _mat_layout(t: torch.Tensor) -> tuple[int, int, int]:
     """(mn_major, ld, batch_stride) of a 2-D/3-D tensor whose last two dims are row- or column-major.
 
@@ -590,6 +620,7 @@ def newton_schulz_bf16(
         kernels = 1
     else:
         kernels = sum(3 if t[2] != 0.0 else 2 for t in schedule)
+    raise_on_earlier_failure(x.device)
     with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
         rc = lib().eo_newton_schulz_bf16(
             x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
@@ -598,6 +629,7 @@ def newton_schulz_bf16(
             ws.data_ptr(), nbytes, scales.data_ptr() if scales is not None else None, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_bf16")
+    note_status(x.device)
     return out
 
 
@@ -615,12 +647,14 @@ def newton_schulz_f32(x: torch.Tensor, schedule) -> torch.Tensor:
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
     abc = (c_float * (3 * len(schedule)))(*[v for t in schedule for v in t])
     kernels = sum(6 if t[2] != 0.0 else 4 for t in schedule)
+    raise_on_earlier_failure(x.device)
     with torch.cuda.device(x.device), _Timed("newton_schulz", kernels, x.device, timed=True):
         rc = lib().eo_newton_schulz_f32(
             x.data_ptr(), batch, rows, cols, ld, bs if x.dim() == 3 else rows * ld, abc, len(schedule),
             out.data_ptr(), cols, rows * cols, ws.data_ptr(), nbytes, _stream(x),
         )  # fmt: skip
     _check(rc, "eo_newton_schulz_f32")
+    note_status(x.device)
     return out
 
 

@@ -445,6 +445,8 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
         return rc;
       p.split_ws = w.ws;
       p.split_cnt = w.cnt;
+      // The kernel leaves its counters at zero, but a launch that gave up a wait may not have: start clean.
+      EO_CUDA(cudaMemsetAsync(w.cnt, 0, split_tiles * 2 * eo::kEpilogueWarps * sizeof(unsigned int), st));
     }
     const int pairs = p.total_tiles < pairs_max ? p.total_tiles : pairs_max;
     eo::eo_gemm_pair_kernel<<<2 * pairs, eo::kGemmThreads, eo::kPairSmemBytes, st>>>(maps, p);

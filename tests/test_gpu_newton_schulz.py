@@ -412,3 +412,20 @@ def test_deferred_normalisation_in_the_per_head_kernel(monkeypatch):
         ref = newton_schulz_torch(x[i], 5, "quintic", bf16=True)
         assert rel_fro(folded[i], ref) <= BF16_TOL and rel_fro(plain[i], ref) <= BF16_TOL
     assert nat.read_device_status() == 0
+
+
+def test_status_mirror_makes_an_earlier_failure_loud():
+    """The mirror of the status word is refreshed by every call; a non-zero value raises at the next call once."""
+    from emerging_optimizers_b200 import _native as nat
+
+    x = randn_tensor(512, 1024, seed=5)
+    with fp32_matmul_precision("medium"):
+        muon_utils.newton_schulz(x, steps=2, coefficient_type="simple")
+        torch.cuda.synchronize()
+        mirror = nat._STATUS_MIRRORS[x.device.index]
+        assert int(mirror[0]) == 0  # the call left a fresh copy of a clean status word
+        mirror[0] = 0x11  # what the copy would hold after a kernel gave up a wait
+        with pytest.raises(nat.NativeLibraryError, match="0x11"):
+            muon_utils.newton_schulz(x, steps=2, coefficient_type="simple")
+        y = muon_utils.newton_schulz(x, steps=2, coefficient_type="simple")  # raised once, works again
+    assert torch.isfinite(y).all()

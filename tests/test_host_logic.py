@@ -315,3 +315,20 @@ def test_padded_buffers_keep_rows_tma_addressable():
     assert c.is_contiguous()
     f = muon_utils._empty_matrix((5, 6), torch.float32, torch.device("cpu"))
     assert f.stride(-2) % 4 == 0
+
+
+def test_a_failed_wait_of_an_earlier_call_raises_at_the_next_call(monkeypatch):
+    """Every Newton-Schulz call mirrors the kernels' status word into host memory; a non-zero mirror (a kernel of
+    an earlier call gave up a bounded wait) makes the next call raise, clears the word and the mirror."""
+    from emerging_optimizers_b200 import _native as nat
+
+    cleared = []
+    monkeypatch.setattr(nat, "read_device_status", lambda device=None: cleared.append(device) or 0x21)
+    dev = torch.device("cuda", 0)
+    monkeypatch.setitem(nat._STATUS_MIRRORS, 0, torch.zeros(1, dtype=torch.int32))
+    nat.raise_on_earlier_failure(dev)  # nothing recorded: passes
+    nat._STATUS_MIRRORS[0][0] = 0x21
+    with pytest.raises(nat.NativeLibraryError, match="0x21"):
+        nat.raise_on_earlier_failure(dev)
+    assert cleared == [dev] and int(nat._STATUS_MIRRORS[0][0]) == 0
+    nat.raise_on_earlier_failure(dev)  # cleared: passes again
