@@ -43,7 +43,7 @@ M, N_COLS, NS_STEPS, COEFF = 8192, 28672, 5, "simple"
 ABC = (3.4445, -4.7750, 2.0315)  # the "simple" tuple
 CPU_SAMPLE = (2048, 7168)  # corner block timed on the host
 NOMINAL_BF16_TFLOPS = 2250.0
-TRAFFIC_BYTES_PER_LAUNCH = 0.67e9
+TRAFFIC_BYTES_PER_LAUNCH = 1.95e9
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 LAYER_SHAPES = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [(4096, 14336)]
 MUON_KW = dict(lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True, weight_decay_method="decoupled",
@@ -508,16 +508,16 @@ def headline_section(ctx: Ctx, args) -> dict:
         "pct_of_nominal_peak_sym": 100.0 * sym * args.steps / sec / 1e12 / NOMINAL_BF16_TFLOPS,
         "roofline": {
             "bound": "tensor",
-            "kernel": "eo_gemm_kernel (the Gram SYRK, A^2 SYRK and BX GEMM launches of one newton_schulz call)",
+            "kernel": "eo_gemm_pair_kernel (the Gram SYRK, A^2 SYRK and BX GEMM launches of one newton_schulz call)",
             "achieved": achieved,
             "peak": sustained,
             "peak_kind": f"bf16_tflops_sustained ({peak_kind}): the launches are timed inside the seconds-long loop",
             "unit": "TFLOP/s",
             "frac": (achieved / sustained) if achieved else None,
             "frac_of_burst_peak": (achieved / burst) if achieved else None,
-            # DRAM bytes per launch: read + write of the Gram, A^2 and BX launches of one iteration measured by
-            # ncu on 4096 x 16384 (138 + 35 + 398 MB), scaled by operand bytes to this shape and averaged over
-            # the three launches.
+            # DRAM bytes per launch: read + write of the Gram, A^2 and BX launches of one iteration of this very
+            # workload measured by ncu (2.09 + 0.60 + 3.17 GB), averaged over the three launches.  The operands
+            # are 0.47 GB (X) and 0.13 GB (A, S): the excess is re-reading by later rounds of tiles.
             "traffic": TRAFFIC_BYTES_PER_LAUNCH if (M, N_COLS) == (8192, 28672) else None,
             "algorithmic_flops_per_launch": sym / per_call_launches if per_call_launches else None,
             "avg_launch_ms": mean_call / per_call_launches if mean_call and per_call_launches else None,
