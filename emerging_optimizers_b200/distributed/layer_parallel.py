@@ -147,6 +147,12 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             GPUs the first step then moves every ``p.data`` into a symmetric buffer owned by this object (a
             collective call; tensors that alias the old storage are not updated any more), and from then on peers
             write the new values straight into that storage.
+            "mixed": per bucket one or the other.  Parameters cost 4 bytes per element of NVLink ingress and nothing
+            else on the receivers; updates cost 2 bytes per element and an HBM-bound weight update on every rank.
+            Both run behind the Newton-Schulz work of the following buckets, and they load different parts of the
+            GPU, so a mixture hides more than either alone when neither hides completely.
+        updates_fraction: with ``exchange="mixed"``, the fraction of the elements (in whole buckets, spread evenly
+            over the step) that travel as updates.
     """
 
     def __init__(
@@ -168,11 +174,14 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         bucket_numel: int = 32 * 1024 * 1024,
         exchange_dtype: torch.dtype | None = None,
         exchange: str = "updates",
+        updates_fraction: float = 0.5,
     ) -> None:
         if num_ns_steps < 1:
             raise ValueError(f"num_ns_steps must be at least 1, got {num_ns_steps}")
-        if exchange not in ("updates", "parameters"):
-            raise ValueError(f"exchange must be 'updates' or 'parameters', got {exchange!r}")
+        if exchange not in ("updates", "parameters", "mixed"):
+            raise ValueError(f"exchange must be 'updates', 'parameters' or 'mixed', got {exchange!r}")
+        if not 0.0 <= updates_fraction <= 1.0:
+            raise ValueError(f"updates_fraction must lie in [0, 1], got {updates_fraction}")
         super().__init__(params, dict(lr=lr, momentum=momentum, weight_decay=weight_decay))
         self.exchange = exchange
         # Flat view of the parameter groups: index i everywhere below is the position in this list, which is also
@@ -195,6 +204,16 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         self.owners = partition_by_cost([ns_cost(p.shape) for p in self.params], self.world)
         self.buckets = _plan_buckets([p.numel() for p in self.params], self.owners, self.world, bucket_numel,
                                      [tuple(p.shape) for p in self.params])  # fmt: skip
+        # exchange="mixed": which buckets travel as updates (error diffusion over the element counts, so that the two
+        # kinds alternate through the step in the requested proportion).
+        self._as_updates = [False] * len(self.buckets)
+        if exchange == "mixed":
+            owed = 0.0
+            for j, b in enumerate(self.buckets):
+                owed += updates_fraction * b.slot_numel
+                if owed >= 0.5 * b.slot_numel:
+                    self._as_updates[j] = True
+                    owed -= b.slot_numel
         self._ns_streams: list = []  # two streams the buckets' Newton-Schulz work alternates between (GPU ranks)
         self._side: "torch.cuda.Stream | None" = None
         self._peer = None  # symmetric exchange buffer, created collectively at the first multi-GPU step
@@ -336,20 +355,13 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
                 self._join_compute_streams(dev)
             return
 
-        if self.exchange == "parameters":
+        if self.exchange in ("parameters", "mixed"):
             self._step_exchanging_parameters(fused, dev)
             return
         if dev.type != "cuda":
             # Host ranks (tests on gloo): plain collective, no overlap.
             for b in self.buckets:
-                slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
-                mine = b.per_rank[self.rank]
-                orths = self._orthogonalize_many([i for i, _ in mine], fused)
-                for i, off in mine:
-                    slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
-                gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
-                dist.all_gather_into_tensor(gathered, slot, group=self.group)
-                self._apply_bucket(b, gathered, fused)
+                self._host_bucket_as_updates(b, fused, dev)
             return
 
         # GPU ranks: the exchange of bucket j (copy-engine pushes into the peers' symmetric buffers, a group
@@ -385,7 +397,17 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         self._join_compute_streams(dev)
         torch.cuda.current_stream().wait_stream(side)
 
-    # -- exchange="parameters" ---------------------------------------------------------------------------
+    def _host_bucket_as_updates(self, b: _Bucket, fused: bool, dev: torch.device) -> None:
+        slot = torch.empty(b.slot_numel, dtype=self.exchange_dtype, device=dev)
+        mine = b.per_rank[self.rank]
+        orths = self._orthogonalize_many([i for i, _ in mine], fused)
+        for i, off in mine:
+            slot[off : off + orths[i].numel()].copy_(orths[i].reshape(-1))
+        gathered = torch.empty(self.world * b.slot_numel, dtype=self.exchange_dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, slot, group=self.group)
+        self._apply_bucket(b, gathered, fused)
+
+    # -- exchange="parameters" and "mixed" ------------------------------------------------------------------
     def _bucket_bases(self) -> list[int]:
         """Element offset of every bucket in the flat parameter buffer (bucket-major, then rank, then slot offset)."""
         bases, at = [], 0
@@ -418,7 +440,10 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
     def _step_exchanging_parameters(self, fused: bool, dev: torch.device) -> None:
         if dev.type != "cuda":
             # Host ranks (tests on gloo): the owners' new values are gathered and copied over the other ranks' copies.
-            for b in self.buckets:
+            for j, b in enumerate(self.buckets):
+                if self._as_updates[j]:
+                    self._host_bucket_as_updates(b, fused, dev)
+                    continue
                 mine = [i for i, _ in b.per_rank[self.rank]]
                 orths = self._orthogonalize_many(mine, fused)
                 self._apply_many(mine, [orths[i] for i in mine], fused)
@@ -442,6 +467,13 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
         if self._param_peer is None:
             self._adopt_parameters(dev)
         peer, side = self._param_peer, self._side
+        max_slot = max([b.slot_numel for j, b in enumerate(self.buckets) if self._as_updates[j]], default=0)
+        if max_slot and self._peer is None:
+            # "mixed": the buckets that travel as updates use the two-halves buffer of exchange="updates" (a half is
+            # rewritten only after the barrier of the exchange in between, see there).
+            from emerging_optimizers_b200.distributed.peer_memory import PeerBuffer
+
+            self._peer = PeerBuffer(2 * self.world * max_slot, self.exchange_dtype, dev, self.group)
         # Entry barrier: a peer may write my copy of its matrices only after everything I enqueued before this step
         # (the backward pass that read them) is done, and symmetrically.
         peer.barrier()
@@ -450,11 +482,22 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             mine = [i for i, _ in b.per_rank[self.rank]]
             with torch.cuda.stream(streams[j % 2]):
                 orths = self._orthogonalize_many(mine, fused)
-                self._apply_many(mine, [orths[i] for i in mine], fused)
+                if not self._as_updates[j]:
+                    self._apply_many(mine, [orths[i] for i in mine], fused)
                 ready = torch.cuda.Event()
                 ready.record()
             with torch.cuda.stream(side):
                 side.wait_event(ready)
+                if self._as_updates[j]:
+                    ubase = (self._exchanges % 2) * self.world * max_slot
+                    self._exchanges += 1
+                    own = ubase + self.rank * b.slot_numel
+                    for i, off in b.per_rank[self.rank]:
+                        self._peer.local[own + off : own + off + orths[i].numel()].copy_(orths[i].reshape(-1))
+                        orths[i].record_stream(side)
+                    self._peer.all_gather_slots(ubase, b.slot_numel)
+                    self._apply_bucket(b, self._peer.local[ubase : ubase + self.world * b.slot_numel], fused)
+                    continue
                 # No barrier per bucket: the buckets' regions are disjoint and nobody reads a pushed matrix before
                 # the step ends, so a rank's pushes never wait for the slowest rank's previous bucket.
                 peer.all_gather_slots(base, b.slot_numel, barrier=PER_BUCKET_BARRIER)

@@ -157,7 +157,7 @@ def _worker_lp(rank, port, out, kw, exchange="updates"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("method,exchange", [("decoupled", "updates"), ("l2", "updates"), ("decoupled", "parameters"), ("l2", "parameters")])
+@pytest.mark.parametrize("method,exchange", [("decoupled", "updates"), ("l2", "updates"), ("decoupled", "parameters"), ("l2", "parameters"), ("decoupled", "mixed")])
 def test_layer_parallel_muon_equals_single_process_bitwise(method, exchange, monkeypatch):
     kw = dict(KW, weight_decay_method=method)
     # single-process specification: this package's Muon with the same injected CPU orthogonalizer

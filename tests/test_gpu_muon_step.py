@@ -145,7 +145,7 @@ def _lp_worker(rank, world, port, out, exchange="updates"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("exchange", ["updates", "parameters"])
+@pytest.mark.parametrize("exchange", ["updates", "parameters", "mixed"])
 def test_layer_parallel_two_gpus_equals_single_process_bitwise(exchange):
     world = 2
     ref_params = _params()
