@@ -711,7 +711,7 @@ def muon_step_section(ctx: Ctx, args) -> dict:
     out.update({
         "what": f"Muon step, Llama-3-8B-shaped parameter set ({layers} layers, {len(params)} matrices, "
         f"{sum(p.numel() for p in params) / 1e9:.2f} G parameters), layer-parallel x{world}, exchange of "
-        f"{args.lp_exchange}{' (updates for %.2f of the elements)' % args.updates_fraction if args.lp_exchange == 'mixed' else ''}"
+        f"{opt.exchange}{' (updates for %.2f of the elements)' % args.updates_fraction if args.lp_exchange == 'mixed' else ''}"
         "; strong scaling",
         "ms": ms, "steps_timed": k, "warmup_steps": parity_steps,
         "tflops_dense_eq": dense / (ms / 1e3) / 1e12, "tflops_sym": sym / (ms / 1e3) / 1e12,
@@ -883,8 +883,9 @@ def main() -> None:
                     help="headline: only the newton_schulz metric, without the secondary sections")
     ap.add_argument("--layers", type=int, default=32, help="layers of the muon_step section")
     ap.add_argument("--muon-steps", type=int, default=5, help="timed steps of the muon_step section")
-    ap.add_argument("--lp-exchange", choices=["updates", "parameters", "mixed"], default="parameters",
-                    help="muon_step: what the layer-parallel optimizer all-gathers")
+    ap.add_argument("--lp-exchange", choices=["auto", "updates", "parameters", "mixed"], default="auto",
+                    help="muon_step: what the layer-parallel optimizer all-gathers (auto: parameters up to four "
+                    "ranks, updates beyond)")
     ap.add_argument("--updates-fraction", type=float, default=0.5,
                     help="muon_step with --lp-exchange mixed: fraction of the elements exchanged as updates")
     ap.add_argument("--bucket-numel", type=int, default=0,

@@ -332,3 +332,17 @@ def test_a_failed_wait_of_an_earlier_call_raises_at_the_next_call(monkeypatch):
         nat.raise_on_earlier_failure(dev)
     assert cleared == [dev] and int(nat._STATUS_MIRRORS[0][0]) == 0
     nat.raise_on_earlier_failure(dev)  # cleared: passes again
+
+
+def test_layer_parallel_exchange_names():
+    from emerging_optimizers_b200.distributed import LayerParallelMuon
+
+    p = [torch.nn.Parameter(torch.zeros(8, 16)) for _ in range(4)]
+    assert LayerParallelMuon(p, exchange="auto").exchange == "parameters"  # one process: a group of one
+    mixed = LayerParallelMuon(p, exchange="mixed", updates_fraction=0.5, bucket_numel=128)
+    assert sum(mixed._as_updates) == len(mixed.buckets) // 2 and len(mixed.buckets) == 4
+    assert not any(LayerParallelMuon(p, exchange="parameters", bucket_numel=128)._as_updates)
+    with pytest.raises(ValueError, match="exchange"):
+        LayerParallelMuon(p, exchange="gradients")
+    with pytest.raises(ValueError, match="updates_fraction"):
+        LayerParallelMuon(p, exchange="mixed", updates_fraction=1.5)
