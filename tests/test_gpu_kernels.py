@@ -267,3 +267,21 @@ def test_split_tail_of_the_pair_kernel(m, n, k, tri, a_mn, b_mn):
         nat.set_option("gemm_split_k", 1)
     assert rel_fro(one.float(), unsplit.float()) <= 2e-3  # both are bf16 roundings of nearly the same fp32 sums
     assert not torch.equal(one, unsplit)  # the split really happened: some roundings differ
+
+
+def test_split_tail_on_two_streams_at_once():
+    """The partial sums of the split tail live in a workspace per stream: products that overlap on two streams must
+    not see each other's pieces."""
+    xs = [(randn_tensor(4352, 15360, seed=40 + i) / 8).bfloat16() for i in range(2)]
+    want = [tk.tsyrk_ex(x) for x in xs]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    got = [[], []]
+    for _ in range(6):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                got[i].append(tk.tsyrk_ex(xs[i]))
+    torch.cuda.synchronize()
+    for i in range(2):
+        for g in got[i]:
+            assert torch.equal(g, want[i])
