@@ -49,7 +49,7 @@ LAYER_SHAPES = [(4096, 4096)] * 2 + [(1024, 4096)] * 2 + [(14336, 4096)] * 2 + [
 MUON_KW = dict(lr=0.02, momentum=0.95, weight_decay=0.1, nesterov=True, weight_decay_method="decoupled",
                num_ns_steps=NS_STEPS, scale_mode="shape_scaling", coefficient_type=COEFF, fp32_matmul_prec="medium",
                use_syrk=True)  # fmt: skip
-HEADS_TOTAL, HEAD_SHAPE, HEAD_CHUNK = 6400, (128, 8192), 800
+HEADS_TOTAL, HEAD_SHAPE, HEAD_CHUNK = 6400, (128, 8192), 1600
 
 
 def flops(m: int, n: int, steps: int) -> tuple[float, float]:
@@ -784,7 +784,7 @@ def tp_section(ctx: Ctx, args) -> dict:
 
 def per_head_section(ctx: Ctx, args) -> dict:
     """BASELINE config 5: 6400 per-head matrices of 128 x 8192 (a Llama-3-70B-shaped attention stack split per
-    head), divided among the N ranks (independent units, no collective), orthogonalized in chunks of 800 by the
+    head), divided among the N ranks (independent units, no collective), orthogonalized in chunks of up to 1600 by the
     fused small-matrix kernel.  One chunk of seeded data is reused for every chunk of a rank."""
     import torch
 
@@ -794,9 +794,10 @@ def per_head_section(ctx: Ctx, args) -> dict:
 
     world, rank, dev = ctx.world, ctx.rank, ctx.dev
     heads_here = HEADS_TOTAL // world
-    chunks = max(1, heads_here // HEAD_CHUNK)
+    chunk = min(HEAD_CHUNK, heads_here)  # matrices per library call (one call runs them as one persistent kernel)
+    chunks = max(1, heads_here // chunk)
     g = torch.Generator(device=dev).manual_seed(4 + rank)
-    x = (torch.randn(HEAD_CHUNK, *HEAD_SHAPE, generator=g, device=dev) * 1e-3).bfloat16().float()
+    x = (torch.randn(chunk, *HEAD_SHAPE, generator=g, device=dev) * 1e-3).bfloat16().float()
 
     def step():
         with fp32_matmul_precision("medium"):
@@ -807,13 +808,13 @@ def per_head_section(ctx: Ctx, args) -> dict:
     ctx.barrier()
     ms = ctx.max_over_ranks(timed(step, 2, 5))[0]
     y = step()
-    err = max(rel_fro(y[i], library_newton_schulz(x[i])) for i in (0, 1, HEAD_CHUNK // 2, HEAD_CHUNK - 1))
+    err = max(rel_fro(y[i], library_newton_schulz(x[i])) for i in (0, 1, chunk // 2, chunk - 1))
     err = ctx.max_over_ranks(err)[0]
     dense, _ = flops(*HEAD_SHAPE, NS_STEPS)
-    total = chunks * HEAD_CHUNK * world
+    total = chunks * chunk * world
     return {
-        "what": f"{total} matrices of {HEAD_SHAPE[0]}x{HEAD_SHAPE[1]} ({chunks * HEAD_CHUNK} per GPU in chunks of "
-        f"{HEAD_CHUNK}), {NS_STEPS} '{COEFF}' steps each, fp32 in/out",
+        "what": f"{total} matrices of {HEAD_SHAPE[0]}x{HEAD_SHAPE[1]} ({chunks * chunk} per GPU in chunks of "
+        f"{chunk}), {NS_STEPS} '{COEFF}' steps each, fp32 in/out",
         "ms": ms,
         "matrices_per_s": total / (ms / 1e3),
         "tflops_dense_eq": total * dense / (ms / 1e3) / 1e12,
