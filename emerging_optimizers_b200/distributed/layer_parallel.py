@@ -149,8 +149,9 @@ class LayerParallelMuon(mixin.WeightDecayMixin, torch.optim.Optimizer):
             write the new values straight into that storage.
             "mixed": per bucket one or the other.  Parameters cost 4 bytes per element of NVLink ingress and nothing
             else on the receivers; updates cost 2 bytes per element and an HBM-bound weight update on every rank.
-            Both run behind the Newton-Schulz work of the following buckets, and they load different parts of the
-            GPU, so a mixture hides more than either alone when neither hides completely.
+            Both run behind the Newton-Schulz work of the following buckets.  On eight B200s a half-and-half
+            mixture measured no better than the better of the two (the step runs at the power cap, where moved
+            bytes cost time wherever they overlap); kept for systems with other ratios of link to HBM speed.
             "auto": "parameters" for groups of up to four ranks, "updates" beyond.  A rank receives
             4 (W - 1) / W bytes per element under "parameters" while its share of the Newton-Schulz work shrinks
             with 1 / W; on eight B200s the 24 GB of pushes per step take 33 - 54 ms alone (box dependent) against
