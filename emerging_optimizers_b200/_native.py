@@ -112,6 +112,7 @@ _PROTOTYPES: dict[str, tuple] = {
         + [c_int, c_int, c_int, c_float, c_float, c_void_p],
     ),
     "eo_peek_device_status_async": (c_int, [c_void_p, c_void_p]),
+    "eo_debug_pair_schedule": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, POINTER(c_int64)]),
     "eo_tp_gram_mirror": (c_int, [c_void_p, c_int, c_int64, c_void_p]),
     "eo_multicast_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "eo_normalize_f32": (
@@ -243,6 +244,22 @@ def note_status(device: torch.device) -> None:
     if mirror is None:
         mirror = _STATUS_MIRRORS[index] = torch.zeros(1, dtype=torch.int32).pin_memory()
     peek_device_status_async(mirror, device)
+
+
+def pair_schedule(M: int, N: int, K: int, tri: bool, batch: int = 1, sm_count: int = 148):
+    """Work items of the CTA-pair kernel for a product of ``batch`` matrices M x N x K as an int32 array of rows
+    ``(matrix, tile row, tile column, first k-block, end k-block, split slot or -1)``; host only, no GPU needed (see
+    ``eo_debug_pair_schedule``)."""
+    import numpy as np
+
+    n = c_int64(0)
+    _check(lib().eo_debug_pair_schedule(M, N, K, int(tri), batch, sm_count, None, 0, ctypes.byref(n)), "schedule")
+    out = np.zeros((n.value, 6), dtype=np.int32)
+    _check(
+        lib().eo_debug_pair_schedule(M, N, K, int(tri), batch, sm_count, out.ctypes.data, n.value, ctypes.byref(n)),
+        "schedule",
+    )
+    return out
 
 
 def _mat_layout(t: torch.Tensor) -> tuple[int, int, int]:

@@ -209,6 +209,47 @@ inline int tp_total_tiles(int N) {
 }
 inline int tp_slots(int N, int world) { return (tp_total_tiles(N) + world - 1) / world; }
 
+// Split tail of the pair kernel: decided from M, N, K and the triangular flag alone (never from the batch size),
+// so that a batched launch and per-matrix launches of the same shape round identically.  It applies when a
+// matrix has at least one and a half rounds of 256 x 256 tiles and its last round is so empty that the K range
+// of those tiles can be cut into two or more pieces that still fit one round.
+void plan_split_tail(int M, int N, int K, int tri, int pairs_max, int* split_s, int* split_rest) {
+  *split_s = 1;
+  *split_rest = 0;
+  const int tm = (M + 255) / 256, tn = (N + 255) / 256;
+  long long tiles1 = 0;
+  if (tri) {
+    for (int j = 0; j < tn; ++j) tiles1 += tm > j ? tm - j : 0;
+  } else {
+    tiles1 = static_cast<long long>(tm) * tn;
+  }
+  const int rest = static_cast<int>(tiles1 % pairs_max);
+  if (2 * tiles1 >= 3LL * pairs_max && rest > 0) {
+    const int num_kb = (K + eo::kBlockK - 1) / eo::kBlockK;
+    int s = pairs_max / rest;
+    if (s > 8) s = 8;
+    // a piece pays for a pipeline fill and a trip of its accumulator through the workspace: keep it long
+    if (s > num_kb / kSplitMinBlocks) s = num_kb / kSplitMinBlocks;
+    if (s >= 2) {
+      *split_s = s;
+      *split_rest = rest;
+    }
+  }
+}
+
+// Work-item schedule of the pair kernel for a launch whose tile counts (256 x 256 tiles) are already in `p`.
+// Returns the number of work items of the whole batch.
+long long fill_pair_schedule(eo::GemmParams& p, int M, int N, int tri, int batch, int split_s, int split_rest) {
+  p.pair_group_m = g_option_pair_group_m;
+  p.pair_band = (tri && M == N && p.tiles_m == p.tiles_n) ? g_option_pair_band : 0;
+  p.pair_hint_a = tri ? 0 : g_option_pair_hint_a;
+  p.pair_hint_b = tri ? 0 : g_option_pair_hint_b;
+  p.split_first = p.tiles_per_batch - split_rest;
+  p.split_s = split_s;
+  p.split_items_per_batch = p.split_first + split_rest * split_s;
+  return static_cast<long long>(p.split_items_per_batch) * batch;
+}
+
 int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t planeA, const void* B, int b_mn,
                 int64_t ldb, int64_t strideB, int64_t planeB, const void* C, int64_t ldc, int64_t strideC, void* D, int64_t ldd, int64_t strideD,
                 int batch, int M, int N, int K, float alpha, float beta, float post_scale, int precision, int d_fp32,
@@ -315,34 +356,11 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   // pay off when every SM still gets several tiles and K is long enough to hide the un-overlapped epilogue.
   p.bm = 128;
   p.stages = eo::kStages;
-  // Split tail of the pair kernel: decided from M, N, K and the triangular flag alone (never from the batch size),
-  // so that a batched launch and per-matrix launches of the same shape round identically.  It applies when a
-  // matrix has at least one and a half rounds of 256 x 256 tiles and its last round is so empty that the K range
-  // of those tiles can be cut into two or more pieces that still fit one round.
   const int pairs_max = dev->sm_count / 2;
   const bool pair_ok = g_option_gemm_pair && tp == nullptr && !d_multicast && precision == 0 && M >= 256 &&
                        N >= 256 && pairs_max >= 1 && g_option_gemm_bm != 128;
   int split_s = 1, split_rest = 0;
-  if (pair_ok && g_option_gemm_split_k) {
-    const int tm = (M + 255) / 256, tn = (N + 255) / 256;
-    long long tiles1 = 0;
-    if (tri) {
-      for (int j = 0; j < tn; ++j) tiles1 += tm > j ? tm - j : 0;
-    } else {
-      tiles1 = static_cast<long long>(tm) * tn;
-    }
-    const int rest = static_cast<int>(tiles1 % pairs_max);
-    if (2 * tiles1 >= 3LL * pairs_max && rest > 0) {
-      int s = pairs_max / rest;
-      if (s > 8) s = 8;
-      // a piece pays for a pipeline fill and a trip of its accumulator through the workspace: keep it long
-      if (s > ((K + bk - 1) / bk) / kSplitMinBlocks) s = ((K + bk - 1) / bk) / kSplitMinBlocks;
-      if (s >= 2) {
-        split_s = s;
-        split_rest = rest;
-      }
-    }
-  }
+  if (pair_ok && g_option_gemm_split_k) plan_split_tail(M, N, K, tri, pairs_max, &split_s, &split_rest);
   if (split_s > 1) {
     p.bm = 256;
     p.stages = 3;
@@ -427,14 +445,7 @@ int launch_gemm(const void* A, int a_mn, int64_t lda, int64_t strideA, int64_t p
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (pair_ok && p.bm == 256 && p.bn == 256) {
     // CTA pairs: one cluster of two CTAs per work item in flight
-    p.pair_group_m = g_option_pair_group_m;
-    p.pair_band = (tri && M == N && p.tiles_m == p.tiles_n) ? g_option_pair_band : 0;
-    p.pair_hint_a = tri ? 0 : g_option_pair_hint_a;
-    p.pair_hint_b = tri ? 0 : g_option_pair_hint_b;
-    p.split_first = p.tiles_per_batch - split_rest;
-    p.split_s = split_s;
-    p.split_items_per_batch = p.split_first + split_rest * split_s;
-    const long long items = static_cast<long long>(p.split_items_per_batch) * batch;
+    const long long items = fill_pair_schedule(p, M, N, tri, batch, split_s, split_rest);
     if (items > 0x3fffffffLL) return fail(EO_ERR_BAD_ARG, "too many tiles");
     p.total_tiles = static_cast<int>(items);
     if (split_rest > 0) {
@@ -472,6 +483,51 @@ extern "C" {
 const char* eo_version(void) { return "eo_b200 0.1.0 sm_100a"; }
 
 const char* eo_last_error(void) { return g_err; }
+
+int eo_debug_pair_schedule(int M, int N, int K, int tri, int batch, int sm_count, int* out, int64_t capacity,
+                           int64_t* n_items) {
+  if (M < 256 || N < 256 || K < 1 || batch < 1 || sm_count < 2 || n_items == nullptr)
+    return fail(EO_ERR_BAD_ARG, "the pair kernel needs M, N >= 256, K, batch >= 1 and at least two SMs");
+  if (tri && M != N) return fail(EO_ERR_BAD_ARG, "a triangular product is square");
+  eo::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.batch = batch;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.tri = tri;
+  p.bm = 256;
+  p.bn = 256;
+  p.tiles_m = (M + 255) / 256;
+  p.tiles_n = (N + 255) / 256;
+  long long per = 0;
+  if (tri) {
+    for (int j = 0; j < p.tiles_n; ++j) per += p.tiles_m > j ? p.tiles_m - j : 0;
+  } else {
+    per = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  }
+  p.tiles_per_batch = static_cast<int>(per);
+  int split_s = 1, split_rest = 0;
+  if (g_option_gemm_split_k) plan_split_tail(M, N, K, tri, sm_count / 2, &split_s, &split_rest);
+  const long long items = fill_pair_schedule(p, M, N, tri, batch, split_s, split_rest);
+  *n_items = items;
+  if (out == nullptr) return EO_OK;
+  if (capacity < items) return fail(EO_ERR_BAD_ARG, "room for %lld work items needed", items);
+  const int num_kb = (K + eo::kBlockK - 1) / eo::kBlockK;
+  for (long long w = 0; w < items; ++w) {
+    const eo::PairWork wk = eo::decode_pair_work(p, static_cast<int>(w), num_kb);
+    int b = 0, ti = 0, tj = 0;
+    eo::decode_pair_tile(p, wk.tile, b, ti, tj);
+    int* row = out + 6 * w;
+    row[0] = b;
+    row[1] = ti;
+    row[2] = tj;
+    row[3] = wk.kb0;
+    row[4] = wk.kb1;
+    row[5] = wk.slot;
+  }
+  return EO_OK;
+}
 
 int eo_set_option(const char* name, int value) {
   if (name == nullptr) return fail(EO_ERR_BAD_ARG, "option name is NULL");

@@ -55,7 +55,7 @@ struct PairWork {
 // shared by several of them comes from DRAM once.  General products: groups of pair_group_m row blocks, column by
 // column inside a group.  Triangular products: bands of pair_band tile columns, row by row inside a band, so that
 // 74 consecutive tiles form a block of about 9 x 8 tiles instead of two whole tile columns.
-__device__ __forceinline__ void decode_pair_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
+__host__ __device__ __forceinline__ void decode_pair_tile(const GemmParams& p, int t, int& b, int& ti, int& tj) {
   b = t / p.tiles_per_batch;
   int r = t - b * p.tiles_per_batch;
   if (p.tri && p.pair_band > 0) {
@@ -95,7 +95,7 @@ __device__ __forceinline__ void decode_pair_tile(const GemmParams& p, int t, int
   }
 }
 
-__device__ __forceinline__ PairWork decode_pair_work(const GemmParams& p, int w, int num_kb) {
+__host__ __device__ __forceinline__ PairWork decode_pair_work(const GemmParams& p, int w, int num_kb) {
   PairWork k;
   const int b = w / p.split_items_per_batch;
   const int r = w - b * p.split_items_per_batch;

@@ -133,7 +133,7 @@ struct GemmParams {
   int pair_hint_b;
 };
 
-__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
+__host__ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int& b, int& ti, int& tj,
                                             const int bm = kBlockM) {
   b = t / p.tiles_per_batch;
   int r = t - b * p.tiles_per_batch;

@@ -58,6 +58,18 @@ const char* eo_last_error(void);
 int eo_set_option(const char* name, int value);
 
 /*
+ * Host-only: the work-item schedule the CTA-pair kernel would follow for a plain bf16 product of `batch` matrices
+ * M x N x K (`tri`: lower-triangular SYRK, M == N) on a GPU with `sm_count` SMs, under the current options.  Uses
+ * the launcher's own planning code and the kernel's own index decoding, compiled for the host; no device is
+ * touched.  Writes the number of work items to *n_items and, if `out` is not NULL (room for `capacity` items of
+ * six ints), per item: matrix, tile row, tile column (256 x 256 tiles), first k-block, one past the last k-block
+ * (64-element blocks), and the index of the split tile the item is a K piece of (-1: a whole tile).  For tests of
+ * the index arithmetic; nothing in the product calls it.
+ */
+int eo_debug_pair_schedule(int M, int N, int K, int tri, int batch, int sm_count, int* out, int64_t capacity,
+                           int64_t* n_items);
+
+/*
  * Reads and clears the status word that kernels of this library write when one of their bounded
  * waits (mbarrier, accumulator hand-off, peer flag) runs out.  Synchronises `stream` first.
  * *host_code receives 0 when every kernel completed normally.
