@@ -18,6 +18,8 @@
 //   tq_full[q]      tile index q published; the leader's producer takes tiles from the global counter, writes the
 //                   index into both CTAs' queues and arrives on both barriers.
 //   tq_empty[q]  L: queue slot q consumed by every role of both CTAs.
+// A queue entry is the work-item index, -1 for "no more work", with bit 30 set when the item belongs to a tile on the
+// diagonal of a SYRK, whose A rows are the CTA's rows of the B operand and are not loaded a second time.
 // Every wait is bounded; a wait that runs out records a code in the status word and the role leaves its loop.
 //
 // Split tail.  Equal tiles run in rounds of one per pair, and the last round of a launch is usually far from full
@@ -43,7 +45,7 @@ constexpr int kSplitHalfFloats = kBlockM * kMaxBlockN;  // one CTA's half of one
 
 // One unit of work: a whole tile, or one K piece of a tile of the split tail.
 struct PairWork {
-  int tile;   // tile index as decode_tile() numbers them (all matrices of the batch)
+  int tile;   // tile index as decode_pair_tile() numbers them (all matrices of the batch)
   int kb0;    // first k-block
   int kb1;    // one past the last k-block
   int slot;   // index of the split tile among all split tiles of the launch, or -1 for a whole tile
