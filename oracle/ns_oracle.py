@@ -194,6 +194,49 @@ def newton_schulz(
     return X
 
 
+def newton_schulz_deferred_norm(
+    x: np.ndarray,
+    steps: int,
+    coefficient_type: str = "quintic",
+    custom_coefficient_sets: Sequence[tuple[float, float, float]] | None = None,
+    eps: float = 1e-15,
+    transpose: bool | None = None,
+) -> np.ndarray:
+    """The bf16 path of :func:`newton_schulz` with the Frobenius normalisation deferred, as the device kernels run
+    it on large matrices: the iterate starts as the un-normalised ``bf16(x)``, and ``s = 1 / max(|x|, eps)`` enters
+    the first iteration's two products instead (``A = bf16(s^2 X X^T)``, ``X' = bf16(s (a X + S X))``).  Not a
+    restatement of the reference (which normalises first, muon_utils.py:242): it states what the variant computes,
+    so that its distance to the reference's results can be measured without a GPU."""
+    x = np.asarray(x)
+    if x.dtype != np.float32 or x.ndim < 2 or x.ndim > 3:
+        raise TypeError("x must be a float32 matrix or stack of matrices")
+    if transpose is None:
+        transpose = x.shape[-2] > x.shape[-1]
+    if transpose:
+        x = _mT(x)
+    f = np.float32
+    sumsq = (x.astype(np.float64) ** 2).sum(axis=(-2, -1), keepdims=True)
+    s = (f(1.0) / np.maximum(np.sqrt(sumsq).astype(np.float32), f(eps))).astype(np.float32)
+    X0 = bf16_round(x)
+    X = None
+    for i, (a, b, c) in enumerate(coefficient_schedule(steps, coefficient_type, custom_coefficient_sets)):
+        if i > 0:
+            X = newton_schulz_step(X, a, b, c, True)
+            continue
+        A = bf16_round((s * s) * np.matmul(X0, _mT(X0)))
+        if c != 0.0:
+            S = bf16_round(f(b) * A + f(c) * np.matmul(A, A))
+            X = bf16_round(s * (f(a) * X0 + np.matmul(S, X0)))
+        else:
+            X = bf16_round(s * (f(a) * X0 + f(b) * np.matmul(A, X0)))
+    if X is None:  # no iteration at all: the normalised input
+        X = bf16_round(s * X0)
+    X = X.astype(np.float32)
+    if transpose:
+        X = _mT(X)
+    return X
+
+
 def newton_schulz_tp_distributed(
     shards: Sequence[np.ndarray],
     steps: int,

@@ -65,6 +65,32 @@ def test_config1_matches_reference(golden_dir):
         assert np.linalg.norm(y.astype(np.float64)) == pytest.approx(float(rec[f"{precision}.fro"]), rel=5e-3)
 
 
+def test_deferred_normalisation_is_as_accurate_on_large_matrices_only(golden_dir):
+    """Why the kernels defer the normalisation only from 2^22 elements per matrix: on the 1024 x 4096 input the
+    variant is as close to the reference's result as the normalise-first path, on the small golden cases single
+    roundings of the un-normalised first iterate show and the 2e-2 bound does not hold."""
+    torch = pytest.importorskip("torch")
+    rec = np.load(os.path.join(golden_dir, "config1.npz"))
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn(1024, 4096, generator=g, dtype=torch.float32).numpy()
+    plain = rel_fro(orc.newton_schulz(x, 5, "simple", precision="medium")[::16, ::16], rec["medium.sample"])
+    deferred = rel_fro(orc.newton_schulz_deferred_norm(x, 5, "simple")[::16, ::16], rec["medium.sample"])
+    assert deferred <= 1.2e-2 and deferred <= 1.1 * plain + 5e-4
+
+    data = np.load(os.path.join(golden_dir, "ns_medium.npz"))
+    cases = json.load(open(os.path.join(golden_dir, "ns_cases.json")))
+    worst = 0.0
+    for name, meta in cases.items():
+        kw = dict(meta["kwargs"])
+        if kw.pop("normalize_in_double", False):
+            continue
+        if "custom_coefficient_sets" in kw:
+            kw["custom_coefficient_sets"] = [tuple(t) for t in kw["custom_coefficient_sets"]]
+        assert data[f"{name}.x"][0].size < (1 << 22) if data[f"{name}.x"].ndim == 3 else data[f"{name}.x"].size < (1 << 22)
+        worst = max(worst, rel_fro(orc.newton_schulz_deferred_norm(data[f"{name}.x"], **kw), data[f"{name}.y"]))
+    assert worst > 2e-2  # below the threshold the reference's rounding points have to be kept
+
+
 def test_muon_step_matches_reference(golden_dir):
     data = np.load(os.path.join(golden_dir, "muon_steps.npz"))
     with open(os.path.join(golden_dir, "muon_cases.json")) as f:
