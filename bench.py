@@ -242,6 +242,8 @@ def bind_host_to_gpu(local_rank: int) -> str:
         if cpus and cpus != allowed:
             os.sched_setaffinity(0, cpus)
             return f"bound to {len(cpus)} cores near the GPU"
+        if not cpus:
+            return f"none of the {len(allowed)} allowed cores is near the GPU"
         return "all allowed cores are near the GPU"
     except Exception as exc:  # noqa: BLE001
         return f"not bound ({type(exc).__name__})"
