@@ -346,3 +346,20 @@ def test_layer_parallel_exchange_names():
         LayerParallelMuon(p, exchange="gradients")
     with pytest.raises(ValueError, match="updates_fraction"):
         LayerParallelMuon(p, exchange="mixed", updates_fraction=1.5)
+
+
+@pytest.mark.parametrize("n", [8, 128, 136, 384, 1000, 2048, 4096, 8192])
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_tensor_parallel_exchange_buffers_hold_every_tile(n, world):
+    """The Gram exchange hands lower-triangle tiles (128 rows x 256 columns, 128 x 128 for n <= 128) to their owners
+    round-robin; the size queries must leave a slot and a flag per (sender, tile) pair on every owner."""
+    from emerging_optimizers_b200 import _native as nat
+
+    lib = nat.lib()
+    tile_n = 256 if n > 128 else 128
+    tm, tn = -(-n // 128), -(-n // tile_n)
+    tiles = sum(1 for i in range(tm) for j in range(tn) if i * 128 + 127 >= j * tile_n)
+    slots = -(-tiles // world)  # tiles per owner
+    assert lib.eo_tp_gram_flag_count(n, world) == world * slots
+    assert lib.eo_tp_gram_inbox_bytes(n, world) == world * slots * 128 * tile_n * 2
+    assert lib.eo_tp_gram_flag_count(0, world) == 0 and lib.eo_tp_gram_inbox_bytes(n, 0) == 0
